@@ -1,0 +1,340 @@
+// C ABI of libokfcuda (include/okf_cuda.h): argument checks, dispatch by type
+// and batch width, host staging for the CPU-operator twins.
+#include <new>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../../include/okf_cuda.h"
+#include "okf_blocks.cuh"
+#include "okf_kernels.h"
+
+using namespace okf;
+
+struct okf_weights {
+    uint8_t *dptr;
+    size_t bytes;
+    bool owned;
+};
+
+struct okf_ctx {
+    int device;
+    cudaStream_t stream;
+    int last_cuda;
+    uint64_t launches;
+    // host-twin staging (device side), grown on demand
+    void *stage_x;
+    size_t stage_x_bytes;
+    void *stage_out;
+    size_t stage_out_bytes;
+    // staged faults (host side only)
+    double fault_rate;
+    uint64_t fault_state;
+};
+
+namespace {
+
+constexpr size_t kTailPad = 256;  // bytes readable past the last block of an upload
+
+int cuda_fail(okf_ctx *ctx, cudaError_t e) {
+    if (ctx) ctx->last_cuda = (int)e;
+    (void)cudaGetLastError();  // clear the sticky-free error so later calls start clean
+    return OKF_E_CUDA;
+}
+
+#define OKF_CUDA(ctx, call)                                   \
+    do {                                                      \
+        cudaError_t e_ = (call);                              \
+        if (e_ != cudaSuccess) return cuda_fail((ctx), e_);   \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+bool type_ok(int ty) { return block_elems(ty) != 0; }
+bool dtype_ok(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
+size_t dtype_size(int dt) { return dt == DT_F32 ? 4 : 2; }
+
+// The seeded draw behind okf_fault_inject: a 64-bit LCG, top 53 bits as a
+// uniform number in [0, 1).
+bool fault_fires(okf_ctx *ctx) {
+    if (ctx->fault_rate <= 0.0) return false;
+    ctx->fault_state = ctx->fault_state * 6364136223846793005ull + 1442695040888963407ull;
+    const double u = (double)(ctx->fault_state >> 11) * (1.0 / 9007199254740992.0);
+    return u < ctx->fault_rate;
+}
+
+int check_tensor(const okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uint32_t k,
+                 uint32_t m) {
+    if (!ctx || !w) return OKF_E_ARG;
+    if (!type_ok(ty)) return OKF_E_TYPE;
+    if (k == 0 || m == 0 || k % (uint32_t)block_elems(ty)) return OKF_E_SHAPE;
+    const uint64_t need = (uint64_t)(k / block_elems(ty)) * block_bytes(ty) * m;
+    if (woff > w->bytes || need > w->bytes - woff) return OKF_E_RANGE;
+    // Q4_K kernels read 32-bit words; the other layouts are 2-byte structured.
+    const uint64_t a = ty == T_Q4_K ? 16 : 2;
+    if (((uintptr_t)w->dptr + woff) % a) return OKF_E_ALIGN;
+    return OKF_OK;
+}
+
+int grow(okf_ctx *ctx, void **buf, size_t *have, size_t need) {
+    if (*have >= need) return OKF_OK;
+    if (*buf) OKF_CUDA(ctx, cudaFree(*buf));
+    *buf = nullptr;
+    *have = 0;
+    cudaError_t e = cudaMalloc(buf, need);
+    if (e == cudaErrorMemoryAllocation) {
+        (void)cudaGetLastError();
+        return OKF_E_NOMEM;
+    }
+    OKF_CUDA(ctx, e);
+    *have = need;
+    return OKF_OK;
+}
+
+int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                  const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream,
+                  bool force_tile) {
+    int rc = check_tensor(ctx, ty, w, woff, k, m);
+    if (rc) return rc;
+    if (!x || !out) return OKF_E_ARG;
+    if (n == 0) return OKF_E_SHAPE;
+    if (!dtype_ok(xdt) || (odt != DT_F32 && odt != DT_BF16)) return OKF_E_TYPE;
+    if ((uintptr_t)x % dtype_size(xdt) || (uintptr_t)out % dtype_size(odt)) return OKF_E_ALIGN;
+    if (fault_fires(ctx)) return OKF_E_INJECTED;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    const uint8_t *wp = w->dptr + woff;
+    cudaError_t e;
+    if (n <= 8 && !force_tile && odt == DT_F32) {
+        e = launch_gemv_simple(ty, wp, k, m, x, xdt, n, (float *)out, s);
+    } else {
+        e = launch_gemm_simple(ty, wp, k, m, x, xdt, n, out, odt, s);
+    }
+    if (e != cudaSuccess) return cuda_fail(ctx, e);
+    ctx->launches++;
+    return OKF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *okf_strerror(int status) {
+    switch (status) {
+    case OKF_OK: return "ok";
+    case OKF_E_ARG: return "bad argument";
+    case OKF_E_TYPE: return "unsupported weight or element type";
+    case OKF_E_SHAPE: return "bad shape: K must be a positive multiple of the block size, M and N positive";
+    case OKF_E_RANGE: return "tensor runs past the end of the weights buffer";
+    case OKF_E_ALIGN: return "pointer or offset not aligned as the kernels need";
+    case OKF_E_CUDA: return "CUDA call failed (see okf_last_cuda_error)";
+    case OKF_E_NOMEM: return "out of memory";
+    case OKF_E_INJECTED: return "staged fault fired (okf_fault_inject)";
+    case OKF_E_LIMIT: return "size beyond a fixed maximum";
+    default: return "unknown status";
+    }
+}
+
+int okf_init(int device, okf_ctx **out) {
+    if (!out) return OKF_E_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        (void)cudaGetLastError();
+        return OKF_E_CUDA;
+    }
+    okf_ctx *ctx = new (std::nothrow) okf_ctx();
+    if (!ctx) return OKF_E_NOMEM;
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device;
+    DeviceGuard g(device);
+    cudaError_t e = g.ok ? cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)
+                         : cudaErrorInvalidDevice;
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        delete ctx;
+        return OKF_E_CUDA;
+    }
+    *out = ctx;
+    return OKF_OK;
+}
+
+void okf_destroy(okf_ctx *ctx) {
+    if (!ctx) return;
+    DeviceGuard g(ctx->device);
+    if (ctx->stream) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+    }
+    if (ctx->stage_x) cudaFree(ctx->stage_x);
+    if (ctx->stage_out) cudaFree(ctx->stage_out);
+    (void)cudaGetLastError();
+    delete ctx;
+}
+
+int okf_last_cuda_error(const okf_ctx *ctx) { return ctx ? ctx->last_cuda : 0; }
+okf_stream okf_ctx_stream(const okf_ctx *ctx) { return ctx ? (okf_stream)ctx->stream : nullptr; }
+uint64_t okf_launch_count(const okf_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int okf_sync(okf_ctx *ctx) {
+    if (!ctx) return OKF_E_ARG;
+    DeviceGuard g(ctx->device);
+    OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return OKF_OK;
+}
+
+int okf_weights_upload(okf_ctx *ctx, const void *host, size_t bytes, okf_weights **out) {
+    if (!ctx || !out || (!host && bytes)) return OKF_E_ARG;
+    *out = nullptr;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    okf_weights *w = new (std::nothrow) okf_weights();
+    if (!w) return OKF_E_NOMEM;
+    w->bytes = bytes;
+    w->owned = true;
+    w->dptr = nullptr;
+    cudaError_t e = cudaMalloc((void **)&w->dptr, bytes + kTailPad);
+    if (e != cudaSuccess) {
+        delete w;
+        if (e == cudaErrorMemoryAllocation) {
+            (void)cudaGetLastError();
+            return OKF_E_NOMEM;
+        }
+        return cuda_fail(ctx, e);
+    }
+    e = cudaMemsetAsync(w->dptr + bytes, 0, kTailPad, ctx->stream);
+    if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(w->dptr, host, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(w->dptr);
+        delete w;
+        return cuda_fail(ctx, e);
+    }
+    *out = w;
+    return OKF_OK;
+}
+
+int okf_weights_wrap(okf_ctx *ctx, const void *device, size_t bytes, okf_weights **out) {
+    if (!ctx || !out || !device) return OKF_E_ARG;
+    okf_weights *w = new (std::nothrow) okf_weights();
+    if (!w) return OKF_E_NOMEM;
+    w->dptr = (uint8_t *)const_cast<void *>(device);
+    w->bytes = bytes;
+    w->owned = false;
+    *out = w;
+    return OKF_OK;
+}
+
+void okf_weights_free(okf_ctx *ctx, okf_weights *w) {
+    if (!w) return;
+    if (w->owned && w->dptr) {
+        DeviceGuard g(ctx ? ctx->device : 0);
+        cudaFree(w->dptr);
+        (void)cudaGetLastError();
+    }
+    delete w;
+}
+
+const void *okf_weights_device_ptr(const okf_weights *w) { return w ? w->dptr : nullptr; }
+size_t okf_weights_bytes(const okf_weights *w) { return w ? w->bytes : 0; }
+
+size_t okf_row_bytes(int type, size_t k) {
+    const int per = block_elems(type);
+    return per ? k / (size_t)per * (size_t)block_bytes(type) : 0;
+}
+
+int okf_gemv(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+             const void *x, int xdt, float *out, okf_stream stream) {
+    return gemm_dispatch(ctx, type, w, woff, k, m, x, xdt, 1, out, DT_F32, stream, false);
+}
+
+int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+             const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream) {
+    return gemm_dispatch(ctx, type, w, woff, k, m, x, xdt, n, out, odt, stream, false);
+}
+
+int okf_gemm_tile(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                  const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream) {
+    return gemm_dispatch(ctx, type, w, woff, k, m, x, xdt, n, out, odt, stream, true);
+}
+
+int okf_dequant(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint64_t count,
+                float *out, okf_stream stream) {
+    if (!ctx || !w || !out) return OKF_E_ARG;
+    if (!type_ok(type)) return OKF_E_TYPE;
+    const uint64_t per = (uint64_t)block_elems(type);
+    if (count % per) return OKF_E_SHAPE;
+    const uint64_t need = count / per * (uint64_t)block_bytes(type);
+    if (woff > w->bytes || need > w->bytes - woff) return OKF_E_RANGE;
+    const uint64_t a = type == T_Q4_K ? 16 : 2;
+    if (((uintptr_t)w->dptr + woff) % a || (uintptr_t)out % 16) return OKF_E_ALIGN;
+    if (count == 0) return OKF_OK;
+    if (fault_fires(ctx)) return OKF_E_INJECTED;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    cudaError_t e = launch_dequant(type, w->dptr + woff, count, out, s);
+    if (e != cudaSuccess) return cuda_fail(ctx, e);
+    ctx->launches++;
+    return OKF_OK;
+}
+
+int okf_matmul_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k,
+                    uint32_t m, const float *x, uint32_t n, float *out) {
+    int rc = check_tensor(ctx, type, w, woff, k, m);
+    if (rc) return rc;
+    if (!x || !out) return OKF_E_ARG;
+    if (n == 0) return OKF_E_SHAPE;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    const size_t xb = (size_t)n * k * sizeof(float), ob = (size_t)n * m * sizeof(float);
+    if ((rc = grow(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb))) return rc;
+    if ((rc = grow(ctx, &ctx->stage_out, &ctx->stage_out_bytes, ob))) return rc;
+    OKF_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = gemm_dispatch(ctx, type, w, woff, k, m, ctx->stage_x, DT_F32, n, ctx->stage_out, DT_F32,
+                       nullptr, false);
+    if (rc) return rc;
+    OKF_CUDA(ctx, cudaMemcpyAsync(out, ctx->stage_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return OKF_OK;
+}
+
+int okf_matvec_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k,
+                    uint32_t m, const float *x, float *out) {
+    return okf_matmul_host(ctx, type, w, woff, k, m, x, 1, out);
+}
+
+int okf_dequant_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint64_t count,
+                     float *out) {
+    if (!ctx || !out) return OKF_E_ARG;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    int rc = grow(ctx, &ctx->stage_out, &ctx->stage_out_bytes, (size_t)count * sizeof(float) + 16);
+    if (rc) return rc;
+    rc = okf_dequant(ctx, type, w, woff, count, (float *)ctx->stage_out, nullptr);
+    if (rc || count == 0) return rc;
+    OKF_CUDA(ctx, cudaMemcpyAsync(out, ctx->stage_out, (size_t)count * sizeof(float),
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+    OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return OKF_OK;
+}
+
+int okf_fault_inject(okf_ctx *ctx, double rate, uint64_t seed) {
+    if (!ctx || !(rate >= 0.0) || rate > 1.0) return OKF_E_ARG;
+    ctx->fault_rate = rate;
+    ctx->fault_state = seed + 0x9E3779B97F4A7C15ull;
+    return OKF_OK;
+}
+
+}  // extern "C"

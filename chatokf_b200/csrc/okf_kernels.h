@@ -1,0 +1,17 @@
+// Launchers of the CUDA kernels, called by the C ABI in okf_api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace okf {
+
+// Simple kernels: one warp per row (matvec), one fp32 register tile per thread
+// (matmul).  They define the numerics the fast kernels are checked against on
+// the device and serve shapes the fast kernels do not take.
+cudaError_t launch_dequant(int ty, const uint8_t *w, uint64_t count, float *out, cudaStream_t s);
+cudaError_t launch_gemv_simple(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x,
+                               int xdt, uint32_t n, float *out, cudaStream_t s);
+cudaError_t launch_gemm_simple(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x,
+                               int xdt, uint32_t n, void *out, int odt, cudaStream_t s);
+
+}  // namespace okf

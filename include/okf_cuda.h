@@ -1,0 +1,150 @@
+/*
+ * okf_cuda.h -- C ABI of libokfcuda: ChatOKF's block-quantized matvec / matmul
+ * operator on NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a Swift module map binds (module.modulemap in this
+ * directory).  Plain pointers and sizes only.  Every entry point returns OKF_OK
+ * (0) or a negative okf_status; nothing aborts or throws.  Device work is
+ * asynchronous on the stream the caller passes unless stated otherwise.
+ *
+ * Data conventions are the reference's (LLM/metal/Kernels.metal:22-24, :112;
+ * LLM/Base/GGUF.swift:49-57, :160-188):
+ *   - weights are native GGUF block bytes, M rows of K/qk blocks, rows
+ *     contiguous, addressed as (weights buffer + woff) with a 64-bit woff;
+ *   - x is [K] (or X is [N][K]), out is [M] (or out[n*M + m]);
+ *   - K must be a multiple of the type's block size; M is arbitrary.
+ *
+ * A context serves one engine thread at a time (like one Metal command
+ * encoder); different contexts may be used from different threads.
+ */
+#ifndef OKF_CUDA_H
+#define OKF_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define OKF_API __attribute__((visibility("default")))
+#else
+#define OKF_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ggml tensor type ids: GGUFType, LLM/Base/GGUF.swift:3-14 */
+typedef enum okf_type {
+    OKF_Q8_0 = 8,     /* 34 B / 32 weights   */
+    OKF_Q4_K = 12,    /* 144 B / 256 weights */
+    OKF_IQ2_XXS = 16, /* 66 B / 256 weights  */
+    OKF_Q2_0 = 42     /* 34 B / 128 weights, ternary */
+} okf_type;
+
+/* element type of activations / outputs */
+typedef enum okf_dtype { OKF_F32 = 0, OKF_F16 = 1, OKF_BF16 = 2 } okf_dtype;
+
+typedef enum okf_status {
+    OKF_OK = 0,
+    OKF_E_ARG = -1,      /* null pointer or otherwise malformed argument      */
+    OKF_E_TYPE = -2,     /* weight or element type not supported (the
+                            reference's fatalError in MetalEnc.swift:108-110,
+                            :144-146 becomes this code)                       */
+    OKF_E_SHAPE = -3,    /* K not a multiple of the block size, N or M zero,
+                            (precondition in LLM/Base/Quant.swift:31)         */
+    OKF_E_RANGE = -4,    /* woff + tensor bytes runs past the weights buffer  */
+    OKF_E_ALIGN = -5,    /* pointer alignment a kernel needs is not met       */
+    OKF_E_CUDA = -6,     /* a CUDA call failed; see okf_last_cuda_error       */
+    OKF_E_NOMEM = -7,    /* host or device allocation failed                  */
+    OKF_E_INJECTED = -8, /* a staged fault from okf_fault_inject fired        */
+    OKF_E_LIMIT = -9     /* a size exceeds a documented fixed maximum         */
+} okf_status;
+
+typedef struct okf_ctx okf_ctx;         /* replaces MetalContext (Base/MetalContext.swift:58-80) */
+typedef struct okf_weights okf_weights; /* replaces WeightRef windows (Base/MetalContext.swift:4-11, :114-185) */
+typedef struct CUstream_st *okf_stream; /* a cudaStream_t; NULL = the context's own stream */
+
+OKF_API const char *okf_strerror(int status);
+
+/* Create a context on `device`: its own stream, host staging, codebook tables
+ * in device memory.  Replaces MetalContext.init (Base/MetalContext.swift:58-80). */
+OKF_API int okf_init(int device, okf_ctx **out);
+OKF_API void okf_destroy(okf_ctx *ctx);
+/* cudaError_t value of the last failed CUDA call on this context (0 if none). */
+OKF_API int okf_last_cuda_error(const okf_ctx *ctx);
+/* The context's stream, for callers that want to order their own work on it. */
+OKF_API okf_stream okf_ctx_stream(const okf_ctx *ctx);
+OKF_API int okf_sync(okf_ctx *ctx);
+
+/* Copy `bytes` of GGUF tensor data (the whole data region, one tensor, or one
+ * row shard) into one device allocation.  Synchronous.  Replaces the zero-copy
+ * buffer windows of MetalContext.cuts/mapped/window (Base/MetalContext.swift:114-185);
+ * woff in the calls below is a byte offset into this buffer, as WeightRef.local is. */
+OKF_API int okf_weights_upload(okf_ctx *ctx, const void *host, size_t bytes, okf_weights **out);
+/* Adopt device memory the caller already owns (no copy, not freed by the
+ * library).  The memory must stay valid while the handle is in use and should
+ * be readable for 256 bytes past `bytes` (kernels may fetch whole 16-byte
+ * words at the tail). */
+OKF_API int okf_weights_wrap(okf_ctx *ctx, const void *device, size_t bytes, okf_weights **out);
+OKF_API void okf_weights_free(okf_ctx *ctx, okf_weights *w);
+OKF_API const void *okf_weights_device_ptr(const okf_weights *w);
+OKF_API size_t okf_weights_bytes(const okf_weights *w);
+
+/* Bytes of one row of K weights: GGUF.rowByteCount (Base/GGUF.swift:160-188).
+ * Returns 0 for an unsupported type. */
+OKF_API size_t okf_row_bytes(int type, size_t k);
+
+/* out[m] = sum_k W[m][k] * x[k].  Replaces MetalEnc.gemv (Base/MetalEnc.swift:84-93)
+ * and its kernels q2_0_gemv / q8_0_gemv / q4_k_gemv / iq2_xxs_gemv
+ * (metal/Kernels.metal:26-109, :1572-1655).  x and out are device pointers;
+ * x holds K elements of xdt, out holds M floats. */
+OKF_API int okf_gemv(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+             const void *x, int xdt, float *out, okf_stream stream);
+
+/* out[n*M + m] = sum_k X[n*K + k] * W[m][k].  Replaces MetalEnc.gemm
+ * (Base/MetalEnc.swift:241-289): N == 1 runs the matvec kernel, 2 <= N <= 8
+ * the narrow (speculative-verify) kernel (gemmNarrowIQ, MetalEnc.swift:222-239),
+ * larger N the tensor-core tile (gemmTiled, MetalEnc.swift:377-400).  X holds
+ * N*K elements of xdt; out holds N*M elements of odt (OKF_F32 or OKF_BF16). */
+OKF_API int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+             const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream);
+
+/* Same contract as okf_gemm but always the tensor-core tile, whatever N is.
+ * Replaces MetalEnc.gemmTile (Base/MetalEnc.swift:326-352), which the
+ * reference's kernel bench uses to time the tile at small N. */
+OKF_API int okf_gemm_tile(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                  const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream);
+
+/* Unpack `count` weights starting at a block boundary (woff) to fp32, bit for
+ * bit what the reference's block decoders produce.  Replaces
+ * MetalEnc.dequantRow (Base/MetalEnc.swift:402-459) and GQ.gather / QB.dequant
+ * (Gemma/Gemma4Quant.swift:320-364, Base/Quant.swift:73-76). */
+OKF_API int okf_dequant(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint64_t count,
+                float *out, okf_stream stream);
+
+/* Host-buffer twins of the CPU operator: QB.matvec (Base/Quant.swift:68-71),
+ * GQ.matmul (Gemma/Gemma4Quant.swift:150-170), QB.dequant (Base/Quant.swift:73-76).
+ * x / out are HOST pointers to fp32; each call copies x to the device, runs the
+ * kernel on the context's stream, copies the result back and waits for it.
+ * Pinned host memory makes the copies asynchronous; pageable memory works. */
+OKF_API int okf_matvec_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k,
+                    uint32_t m, const float *x, float *out);
+OKF_API int okf_matmul_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k,
+                    uint32_t m, const float *x, uint32_t n, float *out);
+OKF_API int okf_dequant_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint64_t count,
+                     float *out);
+
+/* Stage seeded, host-side faults: afterwards each compute call fails with
+ * OKF_E_INJECTED with probability `rate` before anything is launched, so an
+ * engine's retry path can be exercised without disturbing the GPU.  rate 0
+ * switches it off.  Mirrors GPUGate.simulate(thermal:faultRate:seed:)
+ * (Base/MetalGates.swift:101-108). */
+OKF_API int okf_fault_inject(okf_ctx *ctx, double rate, uint64_t seed);
+
+/* Number of kernels this context has launched since it was created. */
+OKF_API uint64_t okf_launch_count(const okf_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OKF_CUDA_H */

@@ -1,0 +1,280 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.
+
+Integer / byte work (dequant) must be bit-exact.  Dot products follow the
+tolerance the task states: max|y - ref| / max|ref| <= 1e-3 against the fp32
+oracle; the tensor-core matmul, which rounds activations and weights to bf16
+tiles, has its own bound (GEMM_TOL) stated below.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from chatokf_b200 import synth
+from chatokf_b200.enc import BF16, F16, F32, CudaEnc, GGUFTensor, OkfError, QB
+from chatokf_b200.gguf_types import GGUFType, block_bytes, block_elems, row_byte_count
+from helpers import ALL_TYPES, golden, lcg_fill, make_weights, rel_err
+
+pytestmark = pytest.mark.gpu
+
+GEMV_TOL = 1e-3   # stated tolerance for fp32-accumulated dot products
+GEMV_TIGHT = 1e-4  # what the reference's own self-test asks of its GPU gemv (QwenMetalSelfTest.swift:580)
+GEMM_TOL = 1e-2   # bf16 operands, fp32 accumulate (the reference accepts 2e-3 for its fp16 tile)
+
+TORCH_DT = {F32: torch.float32, F16: torch.float16, BF16: torch.bfloat16}
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+# ---- dequant: bit-exact ------------------------------------------------------
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+def test_dequant_golden_bits(ctx, ty):
+    g = golden(ty)
+    enc = CudaEnc(ctx)
+    for blocks, bits in ((g["blocks"], g["dequant_bits"]), (g["edge_blocks"], g["edge_dequant_bits"])):
+        w = ctx.upload(blocks)
+        n = blocks.size // block_bytes(ty) * block_elems(ty)
+        out = torch.empty(n, dtype=torch.float32, device="cuda")
+        enc.dequantRow(w, out, n, ty)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), bits)
+
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+def test_dequant_random_blocks_bit_exact(ctx, ty):
+    rng = np.random.default_rng(11)
+    nblk = 100_000 if ty != GGUFType.Q8_0 else 400_000
+    blocks = synth.random_blocks(ty, nblk, rng)
+    want = oracle.dequant(ty, blocks)
+    got = QB(ctx).dequant(GGUFTensor("t", (nblk * block_elems(ty), 1), ty), ctx.upload(blocks), 0, want.size)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+def test_dequant_row_slice(ctx, ty):
+    """dequantRow at a row offset inside a larger buffer (embedding-row read)."""
+    k, m = 1024, 7
+    blocks = make_weights(ty, m, k, seed=5)
+    w = ctx.upload(blocks)
+    t = GGUFTensor("emb", (k, m), ty)
+    full = oracle.dequant(ty, blocks).reshape(m, k)
+    for row in (0, 3, 6):
+        got = QB(ctx).dequant(t, w, row, k)
+        assert np.array_equal(got.view(np.uint32), full[row].view(np.uint32))
+
+
+# ---- matvec ------------------------------------------------------------------
+
+SHAPES = {
+    GGUFType.Q8_0: [(2048, 2048), (96, 37), (32, 5)],
+    GGUFType.Q4_K: [(2560, 512), (9728, 64), (256, 3)],
+    GGUFType.IQ2_XXS: [(5120, 256), (17408, 40), (256, 1)],
+    GGUFType.Q2_0: [(2048, 384), (6144, 130), (128, 9)],
+}
+
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("xdt", [F32, F16, BF16])
+def test_gemv_vs_oracle(ctx, ty, xdt):
+    enc = CudaEnc(ctx)
+    for k, m in SHAPES[ty]:
+        blocks = make_weights(ty, m, k, seed=k + m)
+        x = np.random.default_rng(k).normal(size=k).astype(np.float32)
+        xd = dev(x, TORCH_DT[xdt])
+        xr = xd.float().cpu().numpy()  # the oracle sees exactly the rounded activations
+        ref = oracle.matvec(ty, blocks, k, m, xr)
+        out = torch.full((m + 8,), float("nan"), dtype=torch.float32, device="cuda")
+        enc.gemv(GGUFTensor("w", (k, m), ty), xd, out, ctx.upload(blocks))
+        torch.cuda.synchronize()
+        o = out.cpu().numpy()
+        assert np.isnan(o[m:]).all(), "wrote past the M outputs"
+        assert rel_err(o[:m], ref) <= GEMV_TIGHT, (ty, k, m)
+
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+def test_gemv_golden_fixture(ctx, ty):
+    g = golden(ty)
+    k, m = int(g["k"]), int(g["m"])
+    got = QB(ctx).matvec(GGUFTensor("w", (k, m), ty), ctx.upload(g["blocks"]), g["x"])
+    assert rel_err(got, g["matvec"]) <= GEMV_TIGHT
+
+
+def test_gemv_reference_selftest_shape(ctx):
+    """Config 1 of the benchmark: Q8_0 2048 x 2048 with the LCG activations the
+    reference's self-test uses (QwenMetalSelfTest.swift:593-609)."""
+    k = m = 2048
+    rng = np.random.default_rng(0)
+    blocks = synth.quantize_q8_0(rng.normal(0, 0.02, size=(m, k)).astype(np.float32))
+    x = lcg_fill(k, 1)
+    ref = oracle.matvec(GGUFType.Q8_0, blocks, k, m, x)
+    got = QB(ctx).matvec(GGUFTensor("ffn_gate", (k, m), GGUFType.Q8_0), ctx.upload(blocks), x)
+    assert rel_err(got, ref) <= GEMV_TIGHT
+
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("n", [2, 3, 4, 5, 8])
+def test_narrow_gemm_vs_gemv(ctx, ty, n):
+    """The verify-batch kernel against N single matvecs
+    (QwenMetalSelfTest.swift:448-495) and against the oracle."""
+    k, m = SHAPES[ty][0][0], 200
+    blocks = make_weights(ty, m, k, seed=n)
+    w = ctx.upload(blocks)
+    t = GGUFTensor("w", (k, m), ty)
+    X = np.stack([lcg_fill(k, 70 + c) for c in range(n)])
+    Xd = dev(X)
+    enc = CudaEnc(ctx)
+    out = torch.empty(n, m, dtype=torch.float32, device="cuda")
+    enc.gemm(t, Xd, out, w, n)
+    single = torch.empty(n, m, dtype=torch.float32, device="cuda")
+    for c in range(n):
+        enc.gemv(t, Xd, single, w, x_off_bytes=c * k * 4, out_off_bytes=c * m * 4)
+    torch.cuda.synchronize()
+    assert rel_err(out.cpu().numpy(), single.cpu().numpy()) <= 1e-5
+    assert rel_err(out.cpu().numpy(), oracle.matmul(ty, blocks, k, m, X, n)) <= GEMV_TIGHT
+
+
+# ---- matmul ------------------------------------------------------------------
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("xdt,odt", [(F32, F32), (BF16, F32), (F16, F32), (BF16, BF16)])
+def test_gemm_vs_oracle(ctx, ty, xdt, odt):
+    """N = 33 as in the reference's tile test (QwenMetalSelfTest.swift:396-446),
+    plus a ragged M and an N that is not a multiple of any tile."""
+    enc = CudaEnc(ctx)
+    for k, m, n in [(SHAPES[ty][0][0], 200, 33), (1024, 131, 77)]:
+        blocks = make_weights(ty, m, k, seed=n)
+        X = np.stack([lcg_fill(k, 10 + c) for c in range(n)])
+        Xd = dev(X, TORCH_DT[xdt])
+        ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
+        out = torch.full((n * m + 16,), float("nan"), dtype=TORCH_DT[odt], device="cuda")
+        enc.gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
+        torch.cuda.synchronize()
+        o = out.float().cpu().numpy()
+        assert np.isnan(o[n * m:]).all()
+        tol = GEMM_TOL if odt == F32 else GEMM_TOL + 8e-3  # + bf16 rounding of the result
+        assert rel_err(o[:n * m].reshape(n, m), ref) <= tol, (ty, k, m, n)
+
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+def test_gemm_tile_small_n(ctx, ty):
+    """gemmTile forces the tile kernel at widths the dispatcher would give to
+    the narrow kernel (the reference's kernel bench does this)."""
+    k, m, n = 512, 70, 3
+    blocks = make_weights(ty, m, k, seed=1)
+    X = np.random.default_rng(2).normal(size=(n, k)).astype(np.float32)
+    out = torch.empty(n, m, dtype=torch.float32, device="cuda")
+    CudaEnc(ctx).gemmTile(GGUFTensor("w", (k, m), ty), dev(X), out, ctx.upload(blocks), n)
+    torch.cuda.synchronize()
+    assert rel_err(out.cpu().numpy(), oracle.matmul(ty, blocks, k, m, X, n)) <= GEMM_TOL
+
+
+def test_matmul_host_twin(ctx):
+    ty, k, m, n = GGUFType.Q4_K, 512, 48, 12
+    blocks = make_weights(ty, m, k, seed=9)
+    X = np.random.default_rng(3).normal(size=(n, k)).astype(np.float32)
+    got = QB(ctx).matmul(GGUFTensor("w", (k, m), ty), ctx.upload(blocks), X, n)
+    assert rel_err(got, oracle.matmul(ty, blocks, k, m, X, n)) <= GEMM_TOL
+
+
+# ---- linearity at full size (size-independent property) ------------------------
+
+@pytest.mark.parametrize("ty,k,m", [(GGUFType.Q4_K, 2560, 9728), (GGUFType.Q4_K, 9728, 2560),
+                                    (GGUFType.IQ2_XXS, 5120, 17408), (GGUFType.IQ2_XXS, 17408, 5120),
+                                    (GGUFType.Q2_0, 2048, 6144), (GGUFType.Q8_0, 2048, 2048)])
+def test_full_size_linearity_and_row_spot_checks(ctx, ty, k, m):
+    """At the benchmark's full shapes: W(a*x1 + x2) == a*W x1 + W x2 within the
+    tolerance, and 16 rows picked across M match the oracle run on those rows."""
+    rng = np.random.default_rng(int(ty))
+    blocks = synth.random_blocks(ty, m * k // block_elems(ty), rng)
+    w = ctx.upload(blocks)
+    t = GGUFTensor("w", (k, m), ty)
+    enc = CudaEnc(ctx)
+    x1 = rng.normal(size=k).astype(np.float32)
+    x2 = rng.normal(size=k).astype(np.float32)
+    ys = []
+    for x in (x1, x2, np.float32(0.5) * x1 + x2):
+        out = torch.empty(m, dtype=torch.float32, device="cuda")
+        enc.gemv(t, dev(x), out, w)
+        ys.append(out.cpu().numpy())
+    assert rel_err(ys[2], 0.5 * ys[0] + ys[1]) <= GEMV_TOL
+    rb = row_byte_count(ty, k)
+    rows = np.unique(np.concatenate([[0, m - 1], rng.integers(0, m, size=14)]))
+    br = blocks.reshape(m, rb)
+    ref = oracle.matvec(ty, br[rows].reshape(-1), k, rows.size, x1)
+    assert rel_err(ys[0][rows], ref) <= GEMV_TIGHT
+
+
+# ---- offsets, errors, staged faults --------------------------------------------
+
+def test_woff_addresses_a_tensor_inside_a_larger_buffer(ctx):
+    ty, k, m = GGUFType.Q4_K, 512, 20
+    a = make_weights(ty, m, k, seed=1)
+    b = make_weights(ty, m, k, seed=2)
+    pad = np.zeros(32, dtype=np.uint8)
+    buf = np.concatenate([a, pad, b])
+    w = ctx.upload(buf)
+    x = np.random.default_rng(0).normal(size=k).astype(np.float32)
+    got = QB(ctx).matvec(GGUFTensor("second", (k, m), ty, offset=a.size + 32), w, x)
+    assert rel_err(got, oracle.matvec(ty, b, k, m, x)) <= GEMV_TIGHT
+
+
+def test_error_codes(ctx):
+    ty, k, m = GGUFType.Q4_K, 512, 4
+    w = ctx.upload(make_weights(ty, m, k, seed=1))
+    x = torch.zeros(k, device="cuda")
+    out = torch.zeros(m, device="cuda")
+    enc = CudaEnc(ctx)
+    with pytest.raises(OkfError) as e:
+        enc.gemv(GGUFTensor("w", (k, m), 3), x, out, w)  # q4_1: no kernel
+    assert e.value.status == -2
+    with pytest.raises(OkfError) as e:
+        enc.gemv(GGUFTensor("w", (500, m), ty), x, out, w)  # K not a multiple of 256
+    assert e.value.status == -3
+    with pytest.raises(OkfError) as e:
+        enc.gemv(GGUFTensor("w", (k, m + 1), ty), x, out, w)  # one row too many
+    assert e.value.status == -4
+    with pytest.raises(OkfError) as e:
+        enc.gemv(GGUFTensor("w", (k, 1), ty, offset=8), x, out, w)  # Q4_K needs 16-byte alignment
+    assert e.value.status == -5
+    with pytest.raises(OkfError) as e:
+        enc.gemm(GGUFTensor("w", (k, m), ty), x, out, w, 0)
+    assert e.value.status == -3
+    enc.gemv(GGUFTensor("w", (k, m), ty), x, out, w)  # the context still works
+    torch.cuda.synchronize()
+
+
+def test_staged_faults_are_seeded_and_host_side(ctx):
+    """GPUGate.simulate's contract (LLMTests/GPUGateTests.swift:10-43): the same
+    seed fails the same calls; nothing is launched for a failed call."""
+    ty, k, m = GGUFType.Q8_0, 256, 8
+    w = ctx.upload(make_weights(ty, m, k, seed=1))
+    t = GGUFTensor("w", (k, m), ty)
+    x = torch.ones(k, device="cuda")
+    out = torch.zeros(m, device="cuda")
+    enc = CudaEnc(ctx)
+
+    def run(seed):
+        ctx.fault_inject(0.3, seed)
+        pattern, before = [], ctx.launches
+        for _ in range(40):
+            try:
+                enc.gemv(t, x, out, w)
+                pattern.append(0)
+            except OkfError as e:
+                assert e.status == -8
+                pattern.append(1)
+        launched = ctx.launches - before
+        ctx.fault_inject(0.0, 0)
+        return pattern, launched
+
+    p1, l1 = run(7)
+    p2, _ = run(7)
+    p3, _ = run(8)
+    assert p1 == p2 and p1 != p3
+    assert 0 < sum(p1) < 40 and l1 == 40 - sum(p1)
+    enc.gemv(t, x, out, w)
+    torch.cuda.synchronize()
