@@ -41,6 +41,8 @@ SIGNATURES = {
     "okf_matmul_host": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _u32, _vp]),
     "okf_dequant_host": (_ci, [_vp, _ci, _vp, _u64, _u64, _vp]),
     "okf_fault_inject": (_ci, [_vp, ctypes.c_double, _u64]),
+    "okf_device_status": (_ci, [_vp, ctypes.POINTER(ctypes.c_int)]),
+    "okf_set_flags": (_ci, [_vp, _u32]),
     "okf_launch_count": (_u64, [_vp]),
 }
 

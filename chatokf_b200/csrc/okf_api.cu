@@ -18,6 +18,9 @@ struct okf_weights {
 
 struct okf_ctx {
     int device;
+    int sms;
+    uint32_t flags;
+    int *dev_status;  // device word the kernels' bounded waits report into
     cudaStream_t stream;
     int last_cuda;
     uint64_t launches;
@@ -113,11 +116,19 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
     if (fault_fires(ctx)) return OKF_E_INJECTED;
     DeviceGuard g(ctx->device);
     if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
-    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    cudaStream_t s = (cudaStream_t)stream;
     const uint8_t *wp = w->dptr + woff;
     cudaError_t e;
     if (n <= 8 && !force_tile && odt == DT_F32) {
-        e = launch_gemv_simple(ty, wp, k, m, x, xdt, n, (float *)out, s);
+        const bool simple = ctx->flags & OKF_FLAG_SIMPLE_KERNELS;
+        if (!simple && gemv_fast_supported(ty, k, m, wp, x, xdt, n)) {
+            e = launch_gemv_fast(ty, wp, k, m, x, xdt, n, (float *)out, ctx->dev_status, s, ctx->sms, ctx->device,
+                                 &ctx->launches);
+            if (e != cudaSuccess) return cuda_fail(ctx, e);
+            return OKF_OK;
+        } else {
+            e = launch_gemv_simple(ty, wp, k, m, x, xdt, n, (float *)out, s);
+        }
     } else {
         e = launch_gemm_simple(ty, wp, k, m, x, xdt, n, out, odt, s);
     }
@@ -161,6 +172,9 @@ int okf_init(int device, okf_ctx **out) {
     DeviceGuard g(device);
     cudaError_t e = g.ok ? cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)
                          : cudaErrorInvalidDevice;
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&ctx->sms, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, sizeof(int));
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         delete ctx;
@@ -177,6 +191,7 @@ void okf_destroy(okf_ctx *ctx) {
         cudaStreamSynchronize(ctx->stream);
         cudaStreamDestroy(ctx->stream);
     }
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_out) cudaFree(ctx->stage_out);
     (void)cudaGetLastError();
@@ -283,7 +298,7 @@ int okf_dequant(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uin
     if (fault_fires(ctx)) return OKF_E_INJECTED;
     DeviceGuard g(ctx->device);
     if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
-    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e = launch_dequant(type, w->dptr + woff, count, out, s);
     if (e != cudaSuccess) return cuda_fail(ctx, e);
     ctx->launches++;
@@ -303,7 +318,7 @@ int okf_matmul_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff,
     if ((rc = grow(ctx, &ctx->stage_out, &ctx->stage_out_bytes, ob))) return rc;
     OKF_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x, xb, cudaMemcpyHostToDevice, ctx->stream));
     rc = gemm_dispatch(ctx, type, w, woff, k, m, ctx->stage_x, DT_F32, n, ctx->stage_out, DT_F32,
-                       nullptr, false);
+                       (okf_stream)ctx->stream, false);
     if (rc) return rc;
     OKF_CUDA(ctx, cudaMemcpyAsync(out, ctx->stage_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
     OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -322,11 +337,25 @@ int okf_dequant_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff
     if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
     int rc = grow(ctx, &ctx->stage_out, &ctx->stage_out_bytes, (size_t)count * sizeof(float) + 16);
     if (rc) return rc;
-    rc = okf_dequant(ctx, type, w, woff, count, (float *)ctx->stage_out, nullptr);
+    rc = okf_dequant(ctx, type, w, woff, count, (float *)ctx->stage_out, (okf_stream)ctx->stream);
     if (rc || count == 0) return rc;
     OKF_CUDA(ctx, cudaMemcpyAsync(out, ctx->stage_out, (size_t)count * sizeof(float),
                                   cudaMemcpyDeviceToHost, ctx->stream));
     OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return OKF_OK;
+}
+
+int okf_device_status(okf_ctx *ctx, int *out) {
+    if (!ctx || !out) return OKF_E_ARG;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    OKF_CUDA(ctx, cudaMemcpy(out, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+    return OKF_OK;
+}
+
+int okf_set_flags(okf_ctx *ctx, uint32_t flags) {
+    if (!ctx) return OKF_E_ARG;
+    ctx->flags = flags;
     return OKF_OK;
 }
 

@@ -82,6 +82,16 @@ class Context:
     def launches(self) -> int:
         return int(self.lib.okf_launch_count(self.h))
 
+    def device_status(self) -> int:
+        """0 unless a bounded wait inside a kernel gave up (okf_device_status)."""
+        v = ctypes.c_int(0)
+        self._check(self.lib.okf_device_status(self.h, ctypes.byref(v)), "okf_device_status")
+        return v.value
+
+    def set_flags(self, flags: int):
+        """okf_set_flags: 1 = simple kernels only (device-side yardstick)."""
+        self._check(self.lib.okf_set_flags(self.h, int(flags)), "okf_set_flags")
+
     def fault_inject(self, rate: float, seed: int = 0):
         """GPUGate.simulate(faultRate:seed:), LLM/Base/MetalGates.swift:101-108."""
         self._check(self.lib.okf_fault_inject(self.h, float(rate), int(seed)), "okf_fault_inject")

@@ -62,7 +62,7 @@ typedef enum okf_status {
 
 typedef struct okf_ctx okf_ctx;         /* replaces MetalContext (Base/MetalContext.swift:58-80) */
 typedef struct okf_weights okf_weights; /* replaces WeightRef windows (Base/MetalContext.swift:4-11, :114-185) */
-typedef struct CUstream_st *okf_stream; /* a cudaStream_t; NULL = the context's own stream */
+typedef struct CUstream_st *okf_stream; /* a cudaStream_t; NULL = CUDA's default stream */
 
 OKF_API const char *okf_strerror(int status);
 
@@ -140,6 +140,20 @@ OKF_API int okf_dequant_host(okf_ctx *ctx, int type, const okf_weights *w, uint6
  * switches it off.  Mirrors GPUGate.simulate(thermal:faultRate:seed:)
  * (Base/MetalGates.swift:101-108). */
 OKF_API int okf_fault_inject(okf_ctx *ctx, double rate, uint64_t seed);
+
+/* Waits inside the kernels (on copies landing in shared memory, on other warps)
+ * are bounded; one that gives up writes a non-zero code here and the kernel
+ * returns early with its outputs incomplete.  Synchronous; call it after the
+ * streams that carried the work have been synchronised.  0 = no wait gave up.
+ * The role of the reference's command-buffer error check in GPUGate.verdict
+ * (Base/MetalGates.swift:144-165). */
+OKF_API int okf_device_status(okf_ctx *ctx, int *out);
+
+/* Behaviour switches for testing.  OKF_FLAG_SIMPLE_KERNELS routes every call to
+ * the plain warp-per-row / fp32-tile kernels, which the fast kernels are
+ * checked against on the device.  No counterpart in the reference. */
+#define OKF_FLAG_SIMPLE_KERNELS 1u
+OKF_API int okf_set_flags(okf_ctx *ctx, uint32_t flags);
 
 /* Number of kernels this context has launched since it was created. */
 OKF_API uint64_t okf_launch_count(const okf_ctx *ctx);
