@@ -129,6 +129,8 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
         } else {
             e = launch_gemv_simple(ty, wp, k, m, x, xdt, n, (float *)out, s);
         }
+    } else if (!(ctx->flags & OKF_FLAG_SIMPLE_KERNELS) && gemm_tc_supported(ty, k, m, wp, x, xdt, n)) {
+        e = launch_gemm_tc(ty, wp, k, m, x, xdt, n, out, odt, ctx->dev_status, s, ctx->sms, ctx->device);
     } else {
         e = launch_gemm_simple(ty, wp, k, m, x, xdt, n, out, odt, s);
     }

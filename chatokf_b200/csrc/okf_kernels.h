@@ -22,4 +22,9 @@ cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, c
                              uint32_t n, float *out, int *status, cudaStream_t s, int sms, int dev,
                              uint64_t *launches);
 
+// Prefill matmul on tcgen05 / tensor memory (okf_gemm_tc.cu), any N.
+bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n);
+cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
+                           uint32_t n, void *out, int odt, int *status, cudaStream_t s, int sms, int dev);
+
 }  // namespace okf
