@@ -3,18 +3,21 @@
 // (LLM/metal/Kernels.metal:226-294), which stages fp16 copies of a 64 x 32
 // weight tile and a 32 x 32 activation tile for simdgroup matrices.
 //
-// Shape of the computation.  One CTA owns a 128-row slab of W and walks the
-// tokens in blocks of 256.  Per k-block of 64:
-//   - eight producer warps unpack 128 rows x 64 weights to 16-bit floats and copy
-//     (or convert) 256 tokens x 64 activations, both written K-major into shared
-//     memory in the 128-byte-swizzled layout the tensor core reads;
+// Shape of the computation.  One work item is a 128-row slab of W against one
+// block of 256 tokens or, when more than 256 remain, two such blocks at once so
+// every unpacked weight tile feeds two accumulators.  Per k-block of 64:
+//   - eight warps unpack 128 rows x 64 weights to 16-bit floats and eight more
+//     copy (or convert) 256 tokens x 64 activations, both written K-major into
+//     shared memory in the 128-byte-swizzled layout the tensor core reads.
+//     Weight bytes are fetched one k-block ahead; 16-bit activations go global ->
+//     shared with asynchronous 16-byte copies that signal the stage barrier;
 //   - one thread issues four tcgen05.mma (M = 128, N = 256, K = 16) that
 //     accumulate in fp32 in tensor memory: lane = weight row, column = token;
 //   - tcgen05.commit hands the stage back to the producers when the MMAs that
 //     read it are done.
-// Two 256-column accumulators alternate so the epilogue of one token block
-// (tcgen05.ld, convert, coalesced stores along m) overlaps the next block's
-// main loop.  Operands are fp16 when the activations are fp16, bf16 otherwise
+// The two 256-column accumulators of tensor memory either serve the two token
+// blocks of one item or alternate between items, so an epilogue (tcgen05.ld,
+// convert, coalesced stores along m) overlaps the next main loop.  Operands are fp16 when the activations are fp16, bf16 otherwise
 // (fp32 activations are rounded to bf16); weights are decoded exactly to fp32
 // first and rounded once.
 //
@@ -30,16 +33,15 @@ namespace tc {
 constexpr uint32_t kBM = 128;           // weight rows per CTA tile (UMMA M)
 constexpr uint32_t kBN = 256;           // tokens per accumulator (UMMA N)
 constexpr uint32_t kBK = 64;            // k per stage: 64 x 2 bytes = one 128-byte swizzle row
-constexpr uint32_t kStages = 4;
 constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KB
-constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kProducerWarps = 8;
-constexpr uint32_t kProducers = kProducerWarps * 32;
-constexpr uint32_t kMmaWarp = kProducerWarps;          // warp 8
-constexpr uint32_t kEpiWarp0 = kProducerWarps + 1;     // warps 9..12
-constexpr uint32_t kThreads = (kProducerWarps + 1 + 4) * 32;
-constexpr uint32_t kSmemBytes = 1024 /*align*/ + kStages * kStageBytes + 2048 /*grid*/ + 256 /*barriers*/;
+constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KB per 256 tokens
+constexpr uint32_t kRingBytes = 4 * (kABytes + kBBytes);  // four stages of one token block, or two of two
+constexpr uint32_t kAWarps = 8;                        // warps 0..7 unpack weights (A tile)
+constexpr uint32_t kBWarps = 8;                        // warps 8..15 copy activations (B tile)
+constexpr uint32_t kProducerWarps = kAWarps + kBWarps;
+constexpr uint32_t kMmaWarp = kProducerWarps;          // warp 16
+constexpr uint32_t kThreads = (kProducerWarps + 1 + 4) * 32;  // + MMA warp + four epilogue warps
+constexpr uint32_t kSmemBytes = 1024 /*align*/ + kRingBytes + 2048 /*grid*/ + 256 /*barriers*/;
 constexpr int kStatusGemmTimeout = 3;
 
 struct Args {
@@ -107,31 +109,119 @@ __device__ __forceinline__ uint32_t pack16(float a, float b) {
     }
 }
 
+// ---- weights for the A tile -------------------------------------------------------
+// ARaw<TY> holds, in registers, the bytes one thread needs to unpack 32 weights
+// (half h of k-block kb of its row); load() is issued one k-block ahead of
+// decode() so the memory latency hides behind the previous block's work.
+// Q4_K and Q2_0 (the prefill shapes that are benchmarked) have register
+// forms; the other types unpack straight from memory with decode32.
+template <int TY> struct ARaw {
+    const uint8_t *wp; uint32_t gran;
+    __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) { wp = row; gran = kb * 2 + h; }
+    __device__ __forceinline__ void decode(float (&v)[32], const uint64_t *grid) const { decode32<TY>(wp, gran, v, grid); }
+};
+template <> struct ARaw<T_Q4_K> {
+    uint4 hdr, q0, q1; uint32_t j;  // j: sub-block index 0..7
+    __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) {
+        const uint8_t *b = row + (size_t)(kb >> 2) * 144;
+        hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+        q0 = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 32 * (kb & 3)));
+        q1 = __ldg(reinterpret_cast<const uint4 *>(b + 32 + 32 * (kb & 3)));
+        j = (kb & 3) * 2 + h;
+    }
+    // w = (d * sc) * q - dmin * m (LLM/Quantize/KQuants.swift:104-125), here with one
+    // fused multiply-add: the result is rounded to a 16-bit float anyway
+    __device__ __forceinline__ void decode(float (&v)[32], const uint64_t *) const {
+        const uint32_t s32[3] = {hdr.y, hdr.z, hdr.w};
+        auto sbyte = [&](uint32_t i) { return (s32[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+        uint32_t sc, mn;
+        if (j < 4) { sc = sbyte(j) & 63u; mn = sbyte(j + 4) & 63u; }
+        else { sc = (sbyte(j + 4) & 0xFu) | ((sbyte(j - 4) >> 6) << 4); mn = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4); }
+        const float d1 = f16bits(hdr.x & 0xFFFF) * (float)sc, o1 = f16bits(hdr.x >> 16) * (float)mn;
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t sh = (j & 1) * 4;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t t = (w[i] >> sh) & 0x0F0F0F0Fu;
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[4 * i + e] = fmaf(d1, byte_to_f32(t, e), -o1);
+        }
+    }
+};
+template <> struct ARaw<T_Q2_0> {
+    uint32_t c0, c1, dbits;  // 32 two-bit codes and the block scale
+    __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) {
+        const uint8_t *b = row + (size_t)(kb >> 1) * 34;           // block of 128 weights
+        const uint16_t *q = reinterpret_cast<const uint16_t *>(b + 2 + 16 * (kb & 1) + 8 * h);
+        dbits = __ldg(reinterpret_cast<const uint16_t *>(b));
+        c0 = (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
+        c1 = (uint32_t)__ldg(q + 2) | ((uint32_t)__ldg(q + 3) << 16);
+    }
+    __device__ __forceinline__ void decode(float (&v)[32], const uint64_t *) const {
+        const float d = f16bits(dbits);
+#pragma unroll
+        for (int e = 0; e < 16; e++) {
+            v[e] = (float)((int)((c0 >> (2 * e)) & 3u) - 1) * d;
+            v[16 + e] = (float)((int)((c1 >> (2 * e)) & 3u) - 1) * d;
+        }
+    }
+};
+
 // byte offset of 16-byte chunk j of row r in a 128-byte-swizzled K-major tile
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t j) { return r * 128 + ((j ^ (r & 7)) << 4); }
 
-template <int TY, int XDT, typename OT>
+__device__ __forceinline__ void cp_async16_arrive(uint64_t *bar) {
+    // the arrival fires when this thread's earlier cp.async copies have landed
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One lane polls, the warp follows.  Producers that run ahead sleep between polls
+// so they do not take issue slots from the warps doing the unpacking.
+__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32_t lane, volatile int *abort_flag,
+                                          int *status) {
+    bool ok = true;
+    if (lane == 0) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar, parity)) {
+            __nanosleep(40);
+            if (*abort_flag || clock64() - t0 > kWaitCycles) {
+                if (!*abort_flag) { *abort_flag = 1; if (status) atomicExch(status, kStatusGemmTimeout); }
+                ok = false;
+                break;
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0);
+}
+
+// NACC: token blocks (accumulators) per work item, 1 or 2.
+template <int TY, int XDT, typename OT, int NACC>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
     constexpr bool F16 = XDT == DT_F16;
+    constexpr bool ASYNC_B = XDT != DT_F32;  // 16-bit activations are copied, fp32 ones converted
+    constexpr uint32_t kStageBytes = kABytes + NACC * kBBytes;
+    constexpr uint32_t kStages = kRingBytes / kStageBytes;  // 4 or 2
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *stage0 = smem;
-    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes + 2048);
+    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + kRingBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kRingBytes + 2048);
     uint64_t *full = bars;                     // producers -> MMA, one per stage
-    uint64_t *empty = bars + kStages;          // MMA -> producers
-    uint64_t *acc_full = bars + 2 * kStages;   // MMA -> epilogue, one per accumulator
+    uint64_t *empty = bars + 4;                // MMA -> producers
+    uint64_t *acc_full = bars + 8;             // MMA -> epilogue, one per accumulator
     uint64_t *acc_empty = acc_full + 2;        // epilogue -> MMA
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t m_tiles = (p.m + kBM - 1) / kBM, n_blocks = (p.n + kBN - 1) / kBN;
+    const uint32_t m_tiles = (p.m + kBM - 1) / kBM;
+    const uint32_t n_groups = (p.n + NACC * kBN - 1) / (NACC * kBN);  // token groups of NACC blocks
     const uint32_t kblocks = p.k / kBK;
+    const uint32_t items = m_tiles * n_groups;  // token group fastest: a CTA tends to keep its slab of W
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) {
-            mbar_init(&full[s], kProducerWarps);
+            mbar_init(&full[s], kAWarps + (ASYNC_B ? kBWarps * 32 : kBWarps));
             mbar_init(&empty[s], 1);
         }
         for (uint32_t a = 0; a < 2; a++) {
@@ -154,88 +244,135 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // work items: (m tile, token block) pairs, token block fastest so a CTA keeps its slab of W
-    const uint32_t items = m_tiles * n_blocks;
-
-    if (warp < kProducerWarps) {
-        // ---------------- producers: unpack W, copy X, both into swizzled shared memory
+    if (warp < kAWarps) {
+        // ---------------- A producers: unpack 128 rows x 64 weights into swizzled shared memory
         const uint32_t t = threadIdx.x;
+        const uint32_t arow = t >> 1, ahalf = t & 1;  // thread t unpacks 32 weights of row arow
         uint32_t it = 0;  // running stage counter
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-            const uint32_t mt = item / n_blocks, nb = item % n_blocks;
-            const uint32_t m0 = mt * kBM, n0 = nb * kBN;
-            const uint32_t arow = t >> 1, ahalf = t & 1;  // thread t unpacks 32 weights of row arow
+            const uint32_t m0 = (item / n_groups) * kBM;
             const uint32_t wrow = min(m0 + arow, p.m - 1);
             const uint8_t *wp = p.w + (size_t)wrow * p.row_bytes;
             const bool arow_live = m0 + arow < p.m;
+            ARaw<TY> cur, nxt;
+            cur.load(wp, 0, ahalf);
             for (uint32_t kb = 0; kb < kblocks; kb++, it++) {
                 const uint32_t s = it % kStages, use = it / kStages;
-                if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) goto done;
-                uint8_t *sa = stage0 + (size_t)s * kStageBytes, *sb = sa + kABytes;
-                {   // A: 32 weights -> four 16-byte chunks of row arow
-                    float v[32];
-                    decode32<TY>(wp, kb * 2 + ahalf, v, grid);
+                if (kb + 1 < kblocks) nxt.load(wp, kb + 1, ahalf);
+                float v[32];
+                cur.decode(v, grid);
+                uint4 q[4];
 #pragma unroll
-                    for (int c4 = 0; c4 < 4; c4++) {
-                        uint4 q;
-                        q.x = arow_live ? pack16<F16>(v[8 * c4], v[8 * c4 + 1]) : 0u;
-                        q.y = arow_live ? pack16<F16>(v[8 * c4 + 2], v[8 * c4 + 3]) : 0u;
-                        q.z = arow_live ? pack16<F16>(v[8 * c4 + 4], v[8 * c4 + 5]) : 0u;
-                        q.w = arow_live ? pack16<F16>(v[8 * c4 + 6], v[8 * c4 + 7]) : 0u;
-                        *reinterpret_cast<uint4 *>(sa + swz(arow, ahalf * 4 + c4)) = q;
-                    }
+                for (int c4 = 0; c4 < 4; c4++) {
+                    q[c4].x = arow_live ? pack16<F16>(v[8 * c4], v[8 * c4 + 1]) : 0u;
+                    q[c4].y = arow_live ? pack16<F16>(v[8 * c4 + 2], v[8 * c4 + 3]) : 0u;
+                    q[c4].z = arow_live ? pack16<F16>(v[8 * c4 + 4], v[8 * c4 + 5]) : 0u;
+                    q[c4].w = arow_live ? pack16<F16>(v[8 * c4 + 6], v[8 * c4 + 7]) : 0u;
                 }
-                // B: 256 tokens x 8 chunks, eight chunks per thread
+                if (use > 0 && !warp_wait(&empty[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
+                uint8_t *sa = stage0 + (size_t)s * kStageBytes;
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint32_t q = t + kProducers * i;
-                    const uint32_t row = q >> 3, j = q & 7;
+                for (int c4 = 0; c4 < 4; c4++) *reinterpret_cast<uint4 *>(sa + swz(arow, ahalf * 4 + c4)) = q[c4];
+                fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+                cur = nxt;
+            }
+        }
+    } else if (warp < kProducerWarps) {
+        // ---------------- B producers: NACC x 256 tokens x 64 activations per stage
+        const uint32_t t = threadIdx.x - kAWarps * 32;  // 0..255
+        constexpr uint32_t kChunks = NACC * kBN * 8 / (kBWarps * 32);  // 16-byte chunks per thread: 8 or 16
+        uint32_t it = 0;
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+            const uint32_t n0 = (item % n_groups) * (NACC * kBN);
+            for (uint32_t kb = 0; kb < kblocks; kb++, it++) {
+                const uint32_t s = it % kStages, use = it / kStages;
+                if (use > 0 && !warp_wait(&empty[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
+                uint8_t *sb = stage0 + (size_t)s * kStageBytes + kABytes;
+#pragma unroll
+                for (uint32_t i = 0; i < kChunks; i++) {
+                    const uint32_t q = t + kBWarps * 32 * i;
+                    const uint32_t row = q >> 3, j = q & 7;  // row over NACC x 256 tokens; blocks are 32 KB apart
                     const uint32_t tok = n0 + row;
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (tok < p.n) {
-                        const size_t e = (size_t)tok * p.k + (size_t)kb * kBK + j * 8;
-                        if constexpr (XDT == DT_F32) {
+                    uint8_t *dst = sb + (row >> 8) * kBBytes + swz(row & 255, j);
+                    const size_t e = (size_t)min(tok, p.n - 1) * p.k + (size_t)kb * kBK + j * 8;
+                    if constexpr (ASYNC_B) {
+                        if (tok < p.n) cp_async16(dst, reinterpret_cast<const uint16_t *>(p.x) + e);
+                        else *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+                    } else {
+                        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                        if (tok < p.n) {
                             const float4 f0 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + e));
                             const float4 f1 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + e) + 1);
                             v.x = pack16<false>(f0.x, f0.y); v.y = pack16<false>(f0.z, f0.w);
                             v.z = pack16<false>(f1.x, f1.y); v.w = pack16<false>(f1.z, f1.w);
-                        } else {
-                            v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.x) + e));
                         }
+                        *reinterpret_cast<uint4 *>(dst) = v;
                     }
-                    *reinterpret_cast<uint4 *>(sb + swz(row, j)) = v;
                 }
-                fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full[s]);
+                if constexpr (ASYNC_B) {
+                    cp_async16_arrive(&full[s]);  // every thread: fires when its copies have landed
+                } else {
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full[s]);
+                }
             }
         }
     } else if (warp == kMmaWarp) {
-        // ---------------- MMA issuer: one thread
+        // ---------------- MMA issuer: one thread.  Another lane of the warp asks L2 for the CTA's
+        // whole slab of W (128 contiguous rows) ahead of the producers, which then read it
+        // k-block by k-block, 32 bytes per row at a time.
+        if (lane == 1) {
+            uint32_t last_mt = 0xFFFFFFFFu;
+            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+                const uint32_t mt = item / n_groups;
+                if (mt == last_mt) continue;  // same slab as the previous item
+                last_mt = mt;
+                const uint32_t m0 = mt * kBM;
+                const size_t bytes = (size_t)min(kBM, p.m - m0) * p.row_bytes;
+                const uint8_t *base = p.w + (size_t)m0 * p.row_bytes;
+                if (((uintptr_t)base & 15) == 0) {
+                    for (size_t off = 0; off + 16 <= bytes; off += 32768) {
+                        const uint32_t n = (uint32_t)min((size_t)32768, (bytes - off) & ~(size_t)15);
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(n) : "memory");
+                    }
+                }
+            }
+        }
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(F16 ? 0u : 1u, kBM, kBN);
             uint32_t it = 0, tile = 0;
             for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, tile++) {
-                const uint32_t acc = tile & 1, acc_use = tile >> 1;
-                if (acc_use > 0 && !mbar_wait(&acc_empty[acc], (acc_use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * kBN;
+                // accumulators: both for a two-block item, alternating for one-block items
+                const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
                 bool ok = true;
+                for (uint32_t a = 0; a < (uint32_t)NACC && ok; a++)
+                    if (acc_use > 0) ok = mbar_wait(&acc_empty[acc0 + a], (acc_use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout);
+                if (!ok) break;
+                tc_fence_after();
                 for (uint32_t kb = 0; kb < kblocks; kb++, it++) {
                     const uint32_t s = it % kStages, use = it / kStages;
                     if (!mbar_wait(&full[s], use & 1, abort_flag, p.status, kStatusGemmTimeout)) { ok = false; break; }
+                    fence_proxy_async();  // the asynchronous copies wrote through the generic proxy
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(stage0 + (size_t)s * kStageBytes), sb = sa + kABytes;
-                    const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+                    const uint32_t sa = smem_u32(stage0 + (size_t)s * kStageBytes);
+                    const uint64_t da = smem_desc(sa);
 #pragma unroll
-                    for (uint32_t k4 = 0; k4 < kBK / 16; k4++) {
-                        // 16 k = 32 bytes further along the swizzled 128-byte row
-                        umma(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+                    for (uint32_t a = 0; a < (uint32_t)NACC; a++) {
+                        const uint64_t db = smem_desc(sa + kABytes + a * kBBytes);
+                        const uint32_t d_tmem = tmem_base + (acc0 + a) * kBN;
+#pragma unroll
+                        for (uint32_t k4 = 0; k4 < kBK / 16; k4++) {
+                            // 16 k = 32 bytes further along the swizzled 128-byte row
+                            umma(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
                 }
                 if (!ok) break;
-                umma_commit(&acc_full[acc]);
+                for (uint32_t a = 0; a < (uint32_t)NACC; a++) umma_commit(&acc_full[acc0 + a]);
             }
         }
     } else {
@@ -243,34 +380,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
         const uint32_t q = warp & 3;  // a warp may only touch the lane quarter given by warp id % 4
         uint32_t tile = 0;
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, tile++) {
-            const uint32_t mt = item / n_blocks, nb = item % n_blocks;
-            const uint32_t acc = tile & 1, acc_use = tile >> 1;
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait(&acc_full[acc], acc_use & 1, abort_flag, p.status, kStatusGemmTimeout);
-            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-            tc_fence_after();
+            const uint32_t mt = item / n_groups, n0 = (item % n_groups) * (NACC * kBN);
+            const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
             const uint32_t row = mt * kBM + q * 32 + lane;
             OT *out = reinterpret_cast<OT *>(p.out);
+            for (uint32_t a = 0; a < (uint32_t)NACC; a++) {
+                const uint32_t acc = acc0 + a;
+                if (!warp_wait(&acc_full[acc], acc_use & 1, lane, abort_flag, p.status)) goto done;
+                tc_fence_after();
 #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < kBN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((q * 32) << 16) + acc * kBN + c0, r);
-                tmem_ld_wait();
-                if (row < p.m) {
+                for (uint32_t c0 = 0; c0 < kBN; c0 += 32) {
+                    if (n0 + a * kBN + c0 >= p.n) break;  // nothing but padding from here on
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((q * 32) << 16) + acc * kBN + c0, r);
+                    tmem_ld_wait();
+                    if (row < p.m) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const uint32_t tok = nb * kBN + c0 + j;
-                        if (tok < p.n) {
-                            const float f = __uint_as_float(r[j]);
-                            if constexpr (sizeof(OT) == 4) out[(size_t)tok * p.m + row] = f;
-                            else out[(size_t)tok * p.m + row] = __float2bfloat16_rn(f);
+                        for (int j = 0; j < 32; j++) {
+                            const uint32_t tok = n0 + a * kBN + c0 + j;
+                            if (tok < p.n) {
+                                const float f = __uint_as_float(r[j]);
+                                if constexpr (sizeof(OT) == 4) out[(size_t)tok * p.m + row] = f;
+                                else out[(size_t)tok * p.m + row] = __float2bfloat16_rn(f);
+                            }
                         }
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[acc]);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc]);
         }
     }
 done:
@@ -282,19 +421,30 @@ done:
     }
 }
 
-template <int TY, int XDT, typename OT>
-static cudaError_t launch(const Args &a, cudaStream_t s, int sms, int dev) {
+template <int TY, int XDT, typename OT, int NACC>
+static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
     static bool attr_set[64] = {};  // the opt-in is per device
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TY, XDT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TY, XDT, OT, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    const uint32_t items = ((a.m + kBM - 1) / kBM) * ((a.n + kBN - 1) / kBN);
+    const uint32_t items = ((a.m + kBM - 1) / kBM) * ((a.n + NACC * kBN - 1) / (NACC * kBN));
     const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;
-    gemm_tc_kernel<TY, XDT, OT><<<grid, kThreads, kSmemBytes, s>>>(a);
+    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, kSmemBytes, s>>>(a);
     return cudaGetLastError();
+}
+
+// Two token blocks per item halve the unpacking per flop, but only pay when the
+// slabs alone can fill the GPU; fp32 activations (converted in registers) stay
+// with one block.
+template <int TY, int XDT, typename OT>
+static cudaError_t launch(const Args &a, cudaStream_t s, int sms, int dev) {
+    const uint32_t m_tiles = (a.m + kBM - 1) / kBM;
+    if (XDT != DT_F32 && a.n > kBN && m_tiles * ((a.n + 2 * kBN - 1) / (2 * kBN)) * 10 >= (uint32_t)sms * 9)
+        return launch_n<TY, XDT, OT, 2>(a, s, sms, dev);
+    return launch_n<TY, XDT, OT, 1>(a, s, sms, dev);
 }
 
 template <int TY, int XDT>
