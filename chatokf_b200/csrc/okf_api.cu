@@ -29,6 +29,9 @@ struct okf_ctx {
     size_t stage_x_bytes;
     void *stage_out;
     size_t stage_out_bytes;
+    // scratch for the matmul's k-range partial sums, grown on demand
+    void *scratch;
+    size_t scratch_bytes;
     // staged faults (host side only)
     double fault_rate;
     uint64_t fault_state;
@@ -130,7 +133,21 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
             e = launch_gemv_simple(ty, wp, k, m, x, xdt, n, (float *)out, s);
         }
     } else if (!(ctx->flags & OKF_FLAG_SIMPLE_KERNELS) && gemm_tc_supported(ty, k, m, wp, x, xdt, n)) {
-        e = launch_gemm_tc(ty, wp, k, m, x, xdt, n, out, odt, ctx->dev_status, s, ctx->sms, ctx->device);
+        uint32_t ksplit = gemm_tc_ksplit(k, m, n, xdt, ctx->sms);
+        if (ksplit > 1) {
+            // Growing the scratch allocates, which is not allowed while a stream is being
+            // captured into a graph: size it with one call outside the capture first.
+            const size_t need = (size_t)ksplit * n * m * sizeof(float);
+            if (ctx->scratch_bytes < need) {
+                cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+                (void)cudaStreamIsCapturing(s, &cs);
+                if (cs != cudaStreamCaptureStatusNone) ksplit = 1;
+                else if ((rc = grow(ctx, &ctx->scratch, &ctx->scratch_bytes, need))) return rc;
+            }
+        }
+        e = launch_gemm_tc(ty, wp, k, m, x, xdt, n, out, odt, ctx->dev_status, ksplit, (float *)ctx->scratch, s,
+                           ctx->sms, ctx->device);
+        if (e == cudaSuccess && ksplit > 1) ctx->launches++;
     } else {
         e = launch_gemm_simple(ty, wp, k, m, x, xdt, n, out, odt, s);
     }
@@ -194,6 +211,7 @@ void okf_destroy(okf_ctx *ctx) {
         cudaStreamDestroy(ctx->stream);
     }
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_out) cudaFree(ctx->stage_out);
     (void)cudaGetLastError();

@@ -51,6 +51,8 @@ struct Args {
     int *status;
     uint32_t k, m, n;
     uint32_t row_bytes;
+    uint32_t ksplit;   // work items per (slab, token group): each takes a range of k-blocks
+    float *partial;    // ksplit > 1: fp32 partial results [ksplit][n][m], summed by a second kernel
 };
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -216,8 +218,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (p.m + kBM - 1) / kBM;
     const uint32_t n_groups = (p.n + NACC * kBN - 1) / (NACC * kBN);  // token groups of NACC blocks
-    const uint32_t kblocks = p.k / kBK;
-    const uint32_t items = m_tiles * n_groups;  // token group fastest: a CTA tends to keep its slab of W
+    const uint32_t kblocks_all = p.k / kBK;
+    const uint32_t items = m_tiles * n_groups * p.ksplit;  // k-range fastest, then token group, then slab
+    // item -> slab, token group and the range of k-blocks [kb0, kb0 + kblocks)
+    auto item_mt = [&](uint32_t item) { return item / (n_groups * p.ksplit); };
+    auto item_ng = [&](uint32_t item) { return (item / p.ksplit) % n_groups; };
+    auto item_kb0 = [&](uint32_t item) { return (uint32_t)((uint64_t)kblocks_all * (item % p.ksplit) / p.ksplit); };
+    auto item_kb1 = [&](uint32_t item) { return (uint32_t)((uint64_t)kblocks_all * (item % p.ksplit + 1) / p.ksplit); };
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) {
@@ -250,15 +257,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
         const uint32_t arow = t >> 1, ahalf = t & 1;  // thread t unpacks 32 weights of row arow
         uint32_t it = 0;  // running stage counter
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-            const uint32_t m0 = (item / n_groups) * kBM;
+            const uint32_t m0 = item_mt(item) * kBM;
+            const uint32_t kb0 = item_kb0(item), kb1 = item_kb1(item);
             const uint32_t wrow = min(m0 + arow, p.m - 1);
             const uint8_t *wp = p.w + (size_t)wrow * p.row_bytes;
             const bool arow_live = m0 + arow < p.m;
             ARaw<TY> cur, nxt;
-            cur.load(wp, 0, ahalf);
-            for (uint32_t kb = 0; kb < kblocks; kb++, it++) {
+            cur.load(wp, kb0, ahalf);
+            for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
                 const uint32_t s = it % kStages, use = it / kStages;
-                if (kb + 1 < kblocks) nxt.load(wp, kb + 1, ahalf);
+                if (kb + 1 < kb1) nxt.load(wp, kb + 1, ahalf);
                 float v[32];
                 cur.decode(v, grid);
                 uint4 q[4];
@@ -285,8 +293,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
         constexpr uint32_t kChunks = NACC * kBN * 8 / (kBWarps * 32);  // 16-byte chunks per thread: 8 or 16
         uint32_t it = 0;
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-            const uint32_t n0 = (item % n_groups) * (NACC * kBN);
-            for (uint32_t kb = 0; kb < kblocks; kb++, it++) {
+            const uint32_t n0 = item_ng(item) * (NACC * kBN);
+            const uint32_t kb0 = item_kb0(item), kb1 = item_kb1(item);
+            for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
                 const uint32_t s = it % kStages, use = it / kStages;
                 if (use > 0 && !warp_wait(&empty[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
                 uint8_t *sb = stage0 + (size_t)s * kStageBytes + kABytes;
@@ -327,7 +336,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
         if (lane == 1) {
             uint32_t last_mt = 0xFFFFFFFFu;
             for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-                const uint32_t mt = item / n_groups;
+                const uint32_t mt = item_mt(item);
                 if (mt == last_mt) continue;  // same slab as the previous item
                 last_mt = mt;
                 const uint32_t m0 = mt * kBM;
@@ -352,7 +361,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
                     if (acc_use > 0) ok = mbar_wait(&acc_empty[acc0 + a], (acc_use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout);
                 if (!ok) break;
                 tc_fence_after();
-                for (uint32_t kb = 0; kb < kblocks; kb++, it++) {
+                const uint32_t kb0 = item_kb0(item), kb1 = item_kb1(item);
+                for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
                     const uint32_t s = it % kStages, use = it / kStages;
                     if (!mbar_wait(&full[s], use & 1, abort_flag, p.status, kStatusGemmTimeout)) { ok = false; break; }
                     fence_proxy_async();  // the asynchronous copies wrote through the generic proxy
@@ -366,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
 #pragma unroll
                         for (uint32_t k4 = 0; k4 < kBK / 16; k4++) {
                             // 16 k = 32 bytes further along the swizzled 128-byte row
-                            umma(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+                            umma(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
@@ -380,10 +390,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
         const uint32_t q = warp & 3;  // a warp may only touch the lane quarter given by warp id % 4
         uint32_t tile = 0;
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, tile++) {
-            const uint32_t mt = item / n_groups, n0 = (item % n_groups) * (NACC * kBN);
+            const uint32_t mt = item_mt(item), n0 = item_ng(item) * (NACC * kBN);
             const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
             const uint32_t row = mt * kBM + q * 32 + lane;
             OT *out = reinterpret_cast<OT *>(p.out);
+            float *part = p.ksplit > 1 ? p.partial + (size_t)(item % p.ksplit) * p.n * p.m : nullptr;
             for (uint32_t a = 0; a < (uint32_t)NACC; a++) {
                 const uint32_t acc = acc0 + a;
                 if (!warp_wait(&acc_full[acc], acc_use & 1, lane, abort_flag, p.status)) goto done;
@@ -400,7 +411,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
                             const uint32_t tok = n0 + a * kBN + c0 + j;
                             if (tok < p.n) {
                                 const float f = __uint_as_float(r[j]);
-                                if constexpr (sizeof(OT) == 4) out[(size_t)tok * p.m + row] = f;
+                                if (part) part[(size_t)tok * p.m + row] = f;
+                                else if constexpr (sizeof(OT) == 4) out[(size_t)tok * p.m + row] = f;
                                 else out[(size_t)tok * p.m + row] = __float2bfloat16_rn(f);
                             }
                         }
@@ -421,6 +433,34 @@ done:
     }
 }
 
+// Sum the k-range partials in a fixed order: out[i] = part[0][i] + part[1][i] + ...
+template <typename OT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, OT *__restrict__ out,
+                                                            size_t count, uint32_t ksplit) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < count; i += stride) {
+        if (i + 4 <= count && (count & 3) == 0) {
+            float4 s = *reinterpret_cast<const float4 *>(part + i);
+            for (uint32_t k = 1; k < ksplit; k++) {
+                const float4 v = *reinterpret_cast<const float4 *>(part + k * count + i);
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+            if constexpr (sizeof(OT) == 4) *reinterpret_cast<float4 *>(out + i) = s;
+            else {
+                out[i] = __float2bfloat16_rn(s.x); out[i + 1] = __float2bfloat16_rn(s.y);
+                out[i + 2] = __float2bfloat16_rn(s.z); out[i + 3] = __float2bfloat16_rn(s.w);
+            }
+        } else {
+            for (size_t e = i; e < count && e < i + 4; e++) {
+                float s = part[e];
+                for (uint32_t k = 1; k < ksplit; k++) s += part[k * count + e];
+                if constexpr (sizeof(OT) == 4) out[e] = s;
+                else out[e] = __float2bfloat16_rn(s);
+            }
+        }
+    }
+}
+
 template <int TY, int XDT, typename OT, int NACC>
 static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
     static bool attr_set[64] = {};  // the opt-in is per device
@@ -430,9 +470,13 @@ static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    const uint32_t items = ((a.m + kBM - 1) / kBM) * ((a.n + NACC * kBN - 1) / (NACC * kBN));
+    const uint32_t items = ((a.m + kBM - 1) / kBM) * ((a.n + NACC * kBN - 1) / (NACC * kBN)) * a.ksplit;
     const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;
     gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, kSmemBytes, s>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || a.ksplit == 1) return e;
+    const size_t count = (size_t)a.n * a.m;
+    splitk_reduce_kernel<OT><<<sms * 4, 256, 0, s>>>(a.partial, reinterpret_cast<OT *>(a.out), count, a.ksplit);
     return cudaGetLastError();
 }
 
@@ -441,9 +485,7 @@ static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
 // with one block.
 template <int TY, int XDT, typename OT>
 static cudaError_t launch(const Args &a, cudaStream_t s, int sms, int dev) {
-    const uint32_t m_tiles = (a.m + kBM - 1) / kBM;
-    if (XDT != DT_F32 && a.n > kBN && m_tiles * ((a.n + 2 * kBN - 1) / (2 * kBN)) * 10 >= (uint32_t)sms * 9)
-        return launch_n<TY, XDT, OT, 2>(a, s, sms, dev);
+    if (XDT != DT_F32 && a.n > kBN) return launch_n<TY, XDT, OT, 2>(a, s, sms, dev);
     return launch_n<TY, XDT, OT, 1>(a, s, sms, dev);
 }
 
@@ -466,6 +508,25 @@ static cudaError_t launch_x(const Args &a, int xdt, int odt, cudaStream_t s, int
 
 }  // namespace tc
 
+// How many k-ranges to cut each (slab, token group) into so the work items fill
+// the GPU: the smallest split (up to 8, at least 16 k-blocks each) whose last
+// wave is at least 80 % full, else the fullest one.  A split needs
+// ksplit * n * m floats of scratch for the partial results.
+uint32_t gemm_tc_ksplit(uint32_t k, uint32_t m, uint32_t n, int xdt, int sms) {
+    const uint32_t nacc = (xdt != DT_F32 && n > tc::kBN) ? 2 : 1;
+    const uint32_t base = ((m + tc::kBM - 1) / tc::kBM) * ((n + nacc * tc::kBN - 1) / (nacc * tc::kBN));
+    const uint32_t kblocks = k / tc::kBK;
+    uint32_t best = 1;
+    double best_eff = 0.0;
+    for (uint32_t ks = 1; ks <= 8 && kblocks / ks >= 16; ks++) {
+        const uint32_t items = base * ks, waves = (items + sms - 1) / sms;
+        const double eff = (double)items / ((double)waves * sms);
+        if (eff >= 0.8) return ks;
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
+    }
+    return best;
+}
+
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n) {
     if (ty != T_Q4_K && ty != T_Q8_0 && ty != T_Q2_0 && ty != T_IQ2_XXS) return false;
     if (k % 64 || m == 0 || n == 0) return false;
@@ -475,9 +536,12 @@ bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void
 }
 
 cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
-                           uint32_t n, void *out, int odt, int *status, cudaStream_t s, int sms, int dev) {
+                           uint32_t n, void *out, int odt, int *status, uint32_t ksplit, float *partial,
+                           cudaStream_t s, int sms, int dev) {
     tc::Args a;
     a.w = w; a.x = x; a.out = out; a.status = status; a.k = k; a.m = m; a.n = n;
+    a.ksplit = ksplit > 1 && partial ? ksplit : 1;
+    a.partial = partial;
     a.row_bytes = (k / block_elems(ty)) * block_bytes(ty);
     switch (ty) {
     case T_Q4_K: return tc::launch_x<T_Q4_K>(a, xdt, odt, s, sms, dev);

@@ -24,7 +24,12 @@ cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, c
 
 // Prefill matmul on tcgen05 / tensor memory (okf_gemm_tc.cu), any N.
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n);
+// ksplit > 1 cuts K into ranges whose fp32 partial results go to `partial`
+// (ksplit * n * m floats) and are summed by a second kernel; gemm_tc_ksplit
+// proposes a split for a shape.
+uint32_t gemm_tc_ksplit(uint32_t k, uint32_t m, uint32_t n, int xdt, int sms);
 cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
-                           uint32_t n, void *out, int odt, int *status, cudaStream_t s, int sms, int dev);
+                           uint32_t n, void *out, int odt, int *status, uint32_t ksplit, float *partial,
+                           cudaStream_t s, int sms, int dev);
 
 }  // namespace okf

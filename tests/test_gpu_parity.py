@@ -159,6 +159,24 @@ def test_gemm_vs_oracle(ctx, ty, xdt, odt):
         assert rel_err(o[:n * m].reshape(n, m), ref) <= tol, (ty, k, m, n)
 
 
+def test_gemm_split_k_odd_sizes(ctx):
+    """A short, deep matrix makes the matmul cut K into ranges (partials in
+    scratch, summed by a second kernel); M * N is odd on purpose."""
+    ty, k, m, n = GGUFType.Q4_K, 8192, 131, 45
+    blocks = make_weights(ty, m, k, seed=4)
+    X = np.random.default_rng(5).normal(size=(n, k)).astype(np.float32)
+    Xd = dev(X, torch.bfloat16)
+    ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
+    for odt in (torch.float32, torch.bfloat16):
+        out = torch.full((n * m + 8,), float("nan"), dtype=odt, device="cuda")
+        CudaEnc(ctx).gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
+        torch.cuda.synchronize()
+        o = out.float().cpu().numpy()
+        assert np.isnan(o[n * m:]).all()
+        assert rel_err(o[:n * m].reshape(n, m), ref) <= GEMM_TOL + (8e-3 if odt == torch.bfloat16 else 0)
+    assert ctx.device_status() == 0
+
+
 @pytest.mark.parametrize("ty", ALL_TYPES)
 def test_gemm_tile_small_n(ctx, ty):
     """gemmTile forces the tile kernel at widths the dispatcher would give to
