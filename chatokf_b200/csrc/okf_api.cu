@@ -4,48 +4,15 @@
 #include <stdlib.h>
 #include <string.h>
 
-#include "../../include/okf_cuda.h"
-#include "okf_blocks.cuh"
+#include "okf_internal.h"
 #include "okf_kernels.h"
 
 using namespace okf;
-
-struct okf_weights {
-    uint8_t *dptr;
-    size_t bytes;
-    bool owned;
-};
-
-struct okf_ctx {
-    int device;
-    int sms;
-    uint32_t flags;
-    int *dev_status;  // device word the kernels' bounded waits report into
-    cudaStream_t stream;
-    int last_cuda;
-    uint64_t launches;
-    // host-twin staging (device side), grown on demand
-    void *stage_x;
-    size_t stage_x_bytes;
-    void *stage_out;
-    size_t stage_out_bytes;
-    // scratch for the matmul's k-range partial sums, grown on demand
-    void *scratch;
-    size_t scratch_bytes;
-    // staged faults (host side only)
-    double fault_rate;
-    uint64_t fault_state;
-};
 
 namespace {
 
 constexpr size_t kTailPad = 256;  // bytes readable past the last block of an upload
 
-int cuda_fail(okf_ctx *ctx, cudaError_t e) {
-    if (ctx) ctx->last_cuda = (int)e;
-    (void)cudaGetLastError();  // clear the sticky-free error so later calls start clean
-    return OKF_E_CUDA;
-}
 
 #define OKF_CUDA(ctx, call)                                   \
     do {                                                      \
@@ -53,44 +20,9 @@ int cuda_fail(okf_ctx *ctx, cudaError_t e) {
         if (e_ != cudaSuccess) return cuda_fail((ctx), e_);   \
     } while (0)
 
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = true;
-    explicit DeviceGuard(int dev) {
-        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
-    }
-    ~DeviceGuard() {
-        int cur = -1;
-        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
-    }
-};
 
-bool type_ok(int ty) { return block_elems(ty) != 0; }
-bool dtype_ok(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
-size_t dtype_size(int dt) { return dt == DT_F32 ? 4 : 2; }
 
-// The seeded draw behind okf_fault_inject: a 64-bit LCG, top 53 bits as a
-// uniform number in [0, 1).
-bool fault_fires(okf_ctx *ctx) {
-    if (ctx->fault_rate <= 0.0) return false;
-    ctx->fault_state = ctx->fault_state * 6364136223846793005ull + 1442695040888963407ull;
-    const double u = (double)(ctx->fault_state >> 11) * (1.0 / 9007199254740992.0);
-    return u < ctx->fault_rate;
-}
 
-int check_tensor(const okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uint32_t k,
-                 uint32_t m) {
-    if (!ctx || !w) return OKF_E_ARG;
-    if (!type_ok(ty)) return OKF_E_TYPE;
-    if (k == 0 || m == 0 || k % (uint32_t)block_elems(ty)) return OKF_E_SHAPE;
-    const uint64_t need = (uint64_t)(k / block_elems(ty)) * block_bytes(ty) * m;
-    if (woff > w->bytes || need > w->bytes - woff) return OKF_E_RANGE;
-    // Q4_K kernels read 32-bit words; the other layouts are 2-byte structured.
-    const uint64_t a = ty == T_Q4_K ? 16 : 2;
-    if (((uintptr_t)w->dptr + woff) % a) return OKF_E_ALIGN;
-    return OKF_OK;
-}
 
 int grow(okf_ctx *ctx, void **buf, size_t *have, size_t need) {
     if (*have >= need) return OKF_OK;
@@ -110,12 +42,8 @@ int grow(okf_ctx *ctx, void **buf, size_t *have, size_t need) {
 int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
                   const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream,
                   bool force_tile) {
-    int rc = check_tensor(ctx, ty, w, woff, k, m);
+    int rc = check_gemm_args(ctx, ty, w, woff, k, m, x, xdt, n, out, odt);
     if (rc) return rc;
-    if (!x || !out) return OKF_E_ARG;
-    if (n == 0) return OKF_E_SHAPE;
-    if (!dtype_ok(xdt) || (odt != DT_F32 && odt != DT_BF16)) return OKF_E_TYPE;
-    if ((uintptr_t)x % dtype_size(xdt) || (uintptr_t)out % dtype_size(odt)) return OKF_E_ALIGN;
     if (fault_fires(ctx)) return OKF_E_INJECTED;
     DeviceGuard g(ctx->device);
     if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
