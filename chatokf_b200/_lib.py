@@ -36,6 +36,7 @@ SIGNATURES = {
     "okf_gemv": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _vp, _vp]),
     "okf_gemm": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, _vp, _ci, _vp]),
     "okf_gemm_tile": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, _vp, _ci, _vp]),
+    "okf_gemm_noalloc": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, _vp, _ci, _vp]),
     "okf_dequant": (_ci, [_vp, _ci, _vp, _u64, _u64, _vp, _vp]),
     "okf_matvec_host": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _vp]),
     "okf_matmul_host": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _u32, _vp]),

@@ -24,6 +24,7 @@
 // Every mbarrier wait is bounded (about a second); a wait that gives up records
 // a code in the status word, the CTA frees its tensor memory and returns.
 #include "okf_gemv_mma.cuh"
+#include "okf_internal.h"
 #include "okf_kernels.h"
 
 namespace okf {
@@ -553,3 +554,52 @@ cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, con
 }
 
 }  // namespace okf
+
+// ---- matmul without any allocation ----------------------------------------------------
+// okf_gemm_noalloc serves callers that must not allocate device memory while they
+// run: code inside a CUDA-graph capture or a real-time decode loop, a process that
+// shares the GPU under a fixed memory budget, a plugin host that forbids cudaMalloc
+// after start-up.  The split-K matmul normally takes its partial-sum buffer from
+// the context, which grows it with cudaMalloc on demand; here the buffer is a
+// fixed array that is part of the loaded library image instead.
+namespace okf {
+constexpr size_t kStaticScratchFloats = (size_t)4 << 20;  // 16 MiB on every GPU that loads the library
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+// In host code the name above is only a stand-in for the symbol; the device address has
+// to be asked for, once per device, with that device current.
+static float *g_static_scratch_addr[64] = {};
+}  // namespace okf
+
+extern "C" int okf_gemm_noalloc(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                                const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream) {
+    using namespace okf;
+    int rc = check_gemm_args(ctx, type, w, woff, k, m, x, xdt, n, out, odt);
+    if (rc) return rc;
+    const uint8_t *wp = w->dptr + woff;
+    if (!gemm_tc_supported(type, k, m, wp, x, xdt, n)) return OKF_E_ALIGN;
+    // at least two k-ranges, so the scratch really carries the partial sums
+    if (k / tc::kBK < 2) return OKF_E_SHAPE;
+    uint32_t ksplit = gemm_tc_ksplit(k, m, n, xdt, ctx->sms);
+    if (ksplit < 2) ksplit = 2;
+    const size_t per_split = (size_t)n * m;
+    if (2 * per_split > kStaticScratchFloats) return OKF_E_LIMIT;  // N * M above 2 Mi outputs
+    while (ksplit * per_split > kStaticScratchFloats) ksplit--;
+    if (fault_fires(ctx)) return OKF_E_INJECTED;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    if (ctx->device < 0 || ctx->device >= 64) return OKF_E_ARG;
+    if (!g_static_scratch_addr[ctx->device]) {
+        // first call on this device: resolve the array's device address
+        float *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(ctx, e);
+        g_static_scratch_addr[ctx->device] = ptr;
+    }
+    // every (k-range, token, row) slot the reduction reads is written by the main kernel
+    // first, so nothing in the array has to be cleared between calls
+    cudaError_t e = launch_gemm_tc(type, wp, k, m, x, xdt, n, out, odt, ctx->dev_status, ksplit,
+                                   g_static_scratch_addr[ctx->device], (cudaStream_t)stream, ctx->sms, ctx->device);
+    if (e != cudaSuccess) return cuda_fail(ctx, e);
+    ctx->launches += 2;
+    return OKF_OK;
+}

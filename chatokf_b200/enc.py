@@ -167,6 +167,11 @@ class CudaEnc:
         """MetalEnc.gemmTile: the tensor-core tile at any N (kernel bench)."""
         self._gemm(self.ctx.lib.okf_gemm_tile, "okf_gemm_tile", w, X, out, off, N)
 
+    def gemm_noalloc(self, w: GGUFTensor, X: torch.Tensor, out: torch.Tensor, off: Weights, N: int):
+        """okf_gemm_noalloc: the matmul with its scratch in a fixed array of the library,
+        for callers that may not allocate device memory (N * M <= 2 Mi outputs)."""
+        self._gemm(self.ctx.lib.okf_gemm_noalloc, "okf_gemm_noalloc", w, X, out, off, N)
+
     def dequantRow(self, off: Weights, out: torch.Tensor, n: int, type: int,
                    weight_off: int = 0, out_off_bytes: int = 0):
         """MetalEnc.dequantRow(weightOff:, out:, n:, type:, outOffBytes:)."""

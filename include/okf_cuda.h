@@ -115,6 +115,26 @@ OKF_API int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff
 OKF_API int okf_gemm_tile(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
                   const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream);
 
+/* The same result as okf_gemm, for callers that cannot allocate device memory
+ * while they run (inside a stream capture, in a latency-bound decode loop, under
+ * a host that forbids cudaMalloc after start-up).  It has no counterpart in the
+ * reference.  okf_gemm's tensor-core path keeps the partial sums of its k-ranges
+ * in a buffer the context grows with cudaMalloc when a larger shape arrives; this
+ * entry point uses a fixed 16 MiB array inside the library image instead (every
+ * GPU that loads the library holds it until the process exits) and calls no
+ * allocator of any kind.
+ *   - N * M must not exceed 2 Mi outputs (2 097 152): larger shapes return
+ *     OKF_E_LIMIT.  K must span at least two 64-wide k-blocks, and the pointers
+ *     must meet the tensor-core path's alignment (x 16-byte aligned, K a multiple
+ *     of 64), else OKF_E_SHAPE / OKF_E_ALIGN.
+ *   - The first call on a device looks up the array's device address; make that
+ *     call before any stream capture begins.
+ *   - All calls on a GPU share the one array, whatever context or stream they come
+ *     from: two calls whose kernels overlap on the GPU race on it.  Keep them on
+ *     one stream, or otherwise ordered.  Nothing needs clearing between calls. */
+OKF_API int okf_gemm_noalloc(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                             const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream);
+
 /* Unpack `count` weights starting at a block boundary (woff) to fp32, bit for
  * bit what the reference's block decoders produce.  Replaces
  * MetalEnc.dequantRow (Base/MetalEnc.swift:402-459) and GQ.gather / QB.dequant
