@@ -175,7 +175,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    seed, xdt, mats, layers = WORKLOADS[HEADLINE]
+    seed, xdt, mats, layers = WORKLOADS[args.workload]
     pool = {ty: pool_blocks(ty, seed, 1 << 12) for ty in {m[1] for m in mats}}
     rng = np.random.default_rng(seed + 100)
     xs = [rng.normal(size=k).astype(np.float16).astype(np.float32) for _, _, k, _ in mats]
@@ -190,10 +190,10 @@ def run_reference(args):
     cores = os.cpu_count() or 1
     sample = f"{args.steps} steps x one layer (gate, up, down) of the 64; C restatement of GQ.matvec, {cores} threads"
     print(json.dumps({
-        "impl": "reference", "metric": "quant GEMV HBM GB/s at b=1 (Q4_K FFN triple)", "value": val, "unit": "GB/s",
+        "impl": "reference", "metric": "quant GEMV HBM GB/s at b=1 (%s)" % args.workload, "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": HEADLINE, "batch": 1, "activations": "f16 widened to f32", "layers_per_step": 1},
+        "config": {"workload": args.workload, "batch": 1, "activations": "widened to f32", "layers_per_step": 1},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -353,7 +353,7 @@ def e2e_steps(ctx, L, steps, warmup, torch, dist):
     return sec / steps, h2d, d2h
 
 
-def cpu_baseline(name, budget_s=12.0):
+def cpu_baseline(name, batch=1, budget_s=12.0):
     """Time the oracle (all host threads) on a slice of the workload sized to
     about `budget_s` seconds: a fraction of the rows of one layer's matrices."""
     seed, xdt, mats, _ = WORKLOADS[name]
@@ -368,9 +368,15 @@ def cpu_baseline(name, budget_s=12.0):
         secs += s
         nbytes += b
     cores = os.cpu_count() or 1
+    if batch > 8:
+        # GQ.matmul answers these types as `batch` independent matvecs: same rate per column
+        flops = 2.0 * sum(k * m for _, _, k, m in mats) * reps
+        return {"value": flops / secs / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"{reps} single-column pass(es) over one layer, {secs:.1f} s; GQ.matmul runs these "
+                          f"types as N independent matvecs, so the per-column rate is the matmul rate"}
     return {"value": nbytes / secs / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"{reps} pass(es) over one layer (all rows of gate, up, down) of the 64, {secs:.1f} s; "
-                      f"C restatement of GQ.matvec (the Swift engine does not build on Linux)"}
+            "sample": f"{reps} pass(es) over one layer (all rows of every matrix) of the {WORKLOADS[name][3]}, "
+                      f"{secs:.1f} s; C restatement of GQ.matvec (the Swift engine does not build on Linux)"}
 
 
 def suite_entry(ctx, torch, stream, name, n, pk, steps=20, layers=None, tile=False):
@@ -427,7 +433,9 @@ def run_ours(args):
     ctx = Context(local)
     enc = CudaEnc(ctx)
     stream = torch.cuda.Stream()
-    L = Layers(ctx, HEADLINE, 1, rank, world)
+    wl, batch = args.workload, args.batch
+    L = Layers(ctx, wl, batch, rank, world)
+    tensor_bound = batch > 8
 
     sampler = ClockSampler(local)
     sampler.start()
@@ -454,37 +462,49 @@ def run_ours(args):
 
     ms_step = ms / args.steps
     value = L.bytes_per_step / ms_step / 1e6  # GB/s
+    tflops = L.flops_per_step / ms_step / 1e9
     launches = L.launches_per_step * args.steps  # graph replays launch the captured kernels again
     per_launch_bytes = L.bytes_per_step / L.launches_per_step / world
     per_launch_us = ms_step * 1e3 / L.launches_per_step
 
     e2e_s, h2d, d2h = e2e_steps(ctx, L, max(1, min(args.steps, 10)), args.warmup, torch, dist)
-    e2e_val = L.bytes_per_step / e2e_s / 1e9
+    e2e_val = (L.flops_per_step / e2e_s / 1e12) if tensor_bound else (L.bytes_per_step / e2e_s / 1e9)
 
+    act = {F32: "f32", F16: "f16", BF16: "bf16"}[L.xdt]
+    if tensor_bound:
+        roof = {"bound": "tensor", "achieved": tflops, "peak": pk["tensor"], "unit": "TFLOP/s",
+                "frac": tflops / pk["tensor"], "traffic": TRAFFIC.get(wl), "peak_source": pk["src"] + " (burst)",
+                "flops_per_launch": L.flops_per_step / L.launches_per_step / world,
+                "us_per_launch": per_launch_us, "kernel": "okf gemm_tc (tcgen05)"}
+    else:
+        roof = {"bound": "hbm", "achieved": per_launch_bytes / per_launch_us / 1e3, "peak": pk["hbm"],
+                "unit": "GB/s", "frac": per_launch_bytes / per_launch_us / 1e3 / pk["hbm"],
+                "traffic": TRAFFIC.get(wl), "peak_source": pk["src"],
+                "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us,
+                "kernel": "okf gemv_kernel (decode matvec)"}
     result = {
-        "metric": "quant GEMV HBM GB/s at b=1 (Q4_K FFN triple)", "value": value, "unit": "GB/s",
+        "metric": ("prefill GEMM TFLOP/s" if tensor_bound else "quant GEMV HBM GB/s at b=%d" % batch)
+                  + " (%s)" % wl,
+        "value": tflops if tensor_bound else value, "unit": "TFLOP/s" if tensor_bound else "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": HEADLINE, "batch": 1, "activations": "f16", "layers_per_step": L.layers,
+        "config": {"workload": wl, "batch": batch, "activations": act, "layers_per_step": L.layers,
                    "matrices": [[lab, GGUFType(ty).name, k, m] for lab, ty, k, m in L.full_mats],
                    "weight_bytes_per_step": L.weight_bytes_per_step,
                    "l2": "inputs larger than L2: every layer owns a distinct copy of its weights "
                          f"({L.weight_bytes_per_step / 1e9:.2f} GB per step vs 126 MB L2)",
                    "parallelism": f"rows/{world} + all-gather" if world > 1 else "single GPU",
                    "cuda_graph": graphed},
-        "roofline": {"bound": "hbm", "achieved": per_launch_bytes / per_launch_us / 1e3, "peak": pk["hbm"],
-                     "unit": "GB/s", "frac": per_launch_bytes / per_launch_us / 1e3 / pk["hbm"],
-                     "traffic": TRAFFIC.get(HEADLINE), "peak_source": pk["src"],
-                     "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us,
-                     "kernel": "okf gemv (Q4_K, N=1)"},
-        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+        "roofline": roof,
+        "e2e": {"value": e2e_val, "unit": "TFLOP/s" if tensor_bound else "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3, "api": "okf_matmul_host (QB.matvec twin), one synchronous call per matrix"},
         "gpu_launches": launches,
         "clocks": clocks,
     }
     assert ctx.launches > launches0 or graphed
     if rank == 0 and world == 1:
-        result["cpu_baseline"] = cpu_baseline(HEADLINE)
+        if not args.no_cpu:
+            result["cpu_baseline"] = cpu_baseline(wl, batch)
         if not args.no_suite:
             suite = {}
             plan = [("q8_0_gemv_2048", 1, {}), ("ternary_ffn", 1, {}), ("iq2xxs_trunk", 1, {}),
@@ -520,6 +540,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-suite", action="store_true", help="skip the other configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="which configuration is the timed one")
+    ap.add_argument("--batch", type=int, default=1, help="activation columns (tokens) per call")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
