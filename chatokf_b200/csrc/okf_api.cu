@@ -52,7 +52,7 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
     cudaError_t e;
     if (n <= 8 && !force_tile && odt == DT_F32) {
         const bool simple = ctx->flags & OKF_FLAG_SIMPLE_KERNELS;
-        if (!simple && gemv_fast_supported(ty, k, m, wp, x, xdt, n)) {
+        if (!simple && gemv_fast_supported(ty, k, m, wp, x, xdt, n, ctx->sms)) {
             e = launch_gemv_fast(ty, wp, k, m, x, xdt, n, (float *)out, ctx->dev_status, s, ctx->sms, ctx->device,
                                  &ctx->launches);
             if (e != cudaSuccess) return cuda_fail(ctx, e);

@@ -6,9 +6,10 @@
 // Work split.  A tile is 16 consecutive output rows; a unit is 256 consecutive
 // k of a row (one Q4_K / IQ2_XXS super-block, eight Q8_0 blocks, two Q2_0
 // blocks).  A CTA owns a contiguous range of tiles.  The producer thread brings
-// tiles into a ring of shared-memory stages; when whole rows fit, a stage is 16
-// (or 8) consecutive rows and one contiguous bulk copy, otherwise rows are cut
-// into k-chunks and a stage takes one segment per row.  The eight consumer
+// tiles into a ring of shared-memory stages; when whole rows fit, a stage is a
+// few tiles (or half a tile) of consecutive rows and one contiguous bulk copy,
+// otherwise rows are cut into k-chunks and a stage takes one segment per row.
+// The eight consumer
 // warps deal the units of a stage among themselves, add what they computed
 // into their own slots of a partial-sum buffer, and after a group of tiles the
 // slots are summed in warp order and stored, so results do not depend on
@@ -33,10 +34,12 @@ template <> struct UnitGeom<T_Q2_0> { static constexpr uint32_t bytes = 68; };
 template <> struct UnitGeom<T_IQ2_XXS> { static constexpr uint32_t bytes = 66; };
 
 struct GemvLayout {
-    uint32_t mode;         // 0: stage = 16 whole rows, 1: stage = 8 whole rows, 2: stage = 16 row segments
+    uint32_t mode;         // 0: stage = tps x 16 whole rows, 1: stage = 8 whole rows, 2: stage = 16 row segments
     uint32_t rs;           // bytes between rows inside a stage
     uint32_t stage_bytes;
     uint32_t nstage;       // ring depth
+    uint32_t tps;          // tiles per stage (mode 0 only, else 1)
+    uint32_t ragged;       // mode 2: row segments do not start on 16-byte boundaries
     uint32_t group;        // tiles summed per barrier
     uint32_t nc;           // real activation columns of this pass
     uint32_t ecols;        // effective (fp16) columns staged in shared memory
@@ -373,14 +376,28 @@ __device__ __forceinline__ void stage_x(uint8_t *xs, float *xsum, const GemvLayo
 }
 
 // ---- the kernel ---------------------------------------------------------------------
+// Hooks for a timing harness that includes this file; they compile to nothing here.
+#ifndef OKF_GEMV_TRACE
+#define OKF_GEMV_TRACE_INIT
+#define OKF_GEMV_TRACE(tag)
+#endif
+
+// Position in the ring of stages; the producer and the consumers step through it
+// in the same order, so both keep one of these.
+struct RingPos {
+    uint32_t s = 0, use = 0;  // slot, and how many times the ring wrapped
+    __device__ __forceinline__ void next(uint32_t nstage) {
+        if (++s == nstage) { s = 0; use++; }
+    }
+};
+
 template <int TY, int XDT, bool SEP>
 __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvLayout L) {
     constexpr uint32_t UB = UnitGeom<TY>::bytes;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + kMaxStages;
-    uint64_t *cbar = empty + kMaxStages;  // barrier among the consumer warps
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(cbar + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kMaxStages);
     uint8_t *stages = smem + kBarBytes;
     uint8_t *xs = smem + L.xs_off;
     float *xsum = reinterpret_cast<float *>(smem + L.xsum_off);  // [unit][sub-block][2]
@@ -392,14 +409,15 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     const uint32_t t0 = (uint32_t)((uint64_t)p.tiles * blockIdx.x / gridDim.x);
     const uint32_t t1 = (uint32_t)((uint64_t)p.tiles * (blockIdx.x + 1) / gridDim.x);
     const uint32_t ntl = t1 - t0;
-    const uint32_t spt = L.mode == 1 ? 2 : 1;  // stages per tile per k-chunk
+    const uint32_t spt = L.mode == 1 ? 2 : 1;  // stages per step (two half-tiles in mode 1)
+    OKF_GEMV_TRACE_INIT;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < L.nstage; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kGemvWarps);
         }
-        mbar_init(cbar, kGemvWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -408,51 +426,62 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         for (uint32_t i = threadIdx.x; i < 256; i += kGemvThreads) gw[i] = g_iq2xxs_grid[i];
     }
     __syncthreads();
-    pdl_launch_dependents();
 
-    // Stages are visited in the same order by the producer and the consumers:
-    // group by group, inside a group k-chunk by k-chunk, inside that tile by tile.
+    // Steps are visited in the same order by the producer and the consumers: group
+    // by group, inside a group k-chunk by k-chunk, inside that `tps` tiles at a time.
     if (warp == kGemvWarps) {
-        // ---- producer: weights do not depend on the previous kernel, so no wait here
-        uint32_t si = 0;  // running stage index
+        // ---- producer (one thread): weights do not depend on the previous kernel,
+        // so it does not wait for it
+        if (lane != 0) return;
+        RingPos rp;
+        uint32_t issued = 0;
         for (uint32_t gb = 0; gb < ntl; gb += L.group) {
             const uint32_t gn = min(L.group, ntl - gb);
             for (uint32_t j = 0; j < p.nchunk; j++) {
                 const uint32_t u0 = j * p.cb, nu = min(p.cb, p.nunit - u0);
-                for (uint32_t tl = gb; tl < gb + gn; tl++) {
-                    for (uint32_t half = 0; half < spt; half++, si++) {
-                        const uint32_t s = si % L.nstage, use = si / L.nstage;
-                        const uint32_t row0 = (t0 + tl) * 16 + half * 8;
-                        const uint32_t nrows = row0 < p.m ? min(L.mode == 1 ? 8u : 16u, p.m - row0) : 0u;
-                        // whole-row stages: one copy of nrows rows; the byte count is rounded up
-                        // to 16, which may read a few bytes past the last row (the buffer is padded)
-                        const uint32_t whole_bytes = (nrows * p.row_bytes + 15u) & ~15u;
-                        const uint32_t seg = nu * UB;
-                        bool ok = true;
-                        if (lane == 0) {
-                            if (use > 0) ok = mbar_wait(&empty[s], (use - 1) & 1, abort_flag, p.status, kStatusEmptyTimeout);
-                            if (ok) mbar_expect_tx(&full[s], L.mode == 2 ? seg * 16 : whole_bytes);
-                        }
-                        ok = __shfl_sync(0xffffffffu, ok, 0);
-                        if (!ok) {
+                for (uint32_t tl = gb; tl < gb + gn; tl += L.tps) {
+                    const uint32_t tn = min(L.tps, gb + gn - tl);
+                    for (uint32_t half = 0; half < spt; half++, issued++) {
+                        if (rp.use > 0 &&
+                            !mbar_wait(&empty[rp.s], (rp.use - 1) & 1, abort_flag, p.status, kStatusEmptyTimeout)) {
                             // giving up: let the copies already issued land before the CTA goes away
-                            if (lane == 0) {
-                                const uint32_t first = si > L.nstage ? si - L.nstage : 0;
-                                for (uint32_t d = first; d < si; d++) {
-                                    bool landed = false;
-                                    for (uint32_t i = 0; i < kSpinLimit && !landed; i++)
-                                        landed = mbar_try_wait(&full[d % L.nstage], (d / L.nstage) & 1);
-                                }
+                            const uint32_t first = issued > L.nstage ? issued - L.nstage : 0;
+                            for (uint32_t d = first; d < issued; d++) {
+                                bool landed = false;
+                                for (uint32_t i = 0; i < kSpinLimit && !landed; i++)
+                                    landed = mbar_try_wait(&full[d % L.nstage], (d / L.nstage) & 1);
                             }
                             return;
                         }
-                        uint8_t *dst = stages + (size_t)s * L.stage_bytes;
+                        const uint32_t row0 = (t0 + tl) * 16 + half * 8;
+                        uint8_t *dst = stages + (size_t)rp.s * L.stage_bytes;
                         if (L.mode != 2) {
-                            if (lane == 0 && whole_bytes) bulk_g2s(dst, p.w + (size_t)row0 * p.row_bytes, whole_bytes, &full[s]);
-                        } else if (lane < 16) {
-                            const uint32_t row = min(row0 + lane, p.m - 1);
-                            bulk_g2s(dst + (size_t)lane * L.rs, p.w + (size_t)row * p.row_bytes + (size_t)u0 * UB, seg, &full[s]);
+                            // whole rows: one copy; the byte count is rounded up to 16, which may
+                            // read a few bytes past the last row (weight buffers are padded)
+                            const uint32_t want = L.mode == 1 ? 8u : 16u * tn;
+                            const uint32_t nrows = row0 < p.m ? min(want, p.m - row0) : 0u;
+                            const uint32_t bytes = (nrows * p.row_bytes + 15u) & ~15u;
+                            mbar_expect_tx(&full[rp.s], bytes);
+                            if (bytes) bulk_g2s(dst, p.w + (size_t)row0 * p.row_bytes, bytes, &full[rp.s]);
+                        } else {
+                            // one copy per row segment.  A segment may start anywhere (2-byte
+                            // aligned layouts): the copy starts at the 16-byte boundary below it
+                            // and the consumers skip the same few bytes.
+                            const uint32_t seg = nu * UB;
+                            uint32_t total = 0;
+                            for (uint32_t r = 0; r < 16; r++) {
+                                const size_t src = (size_t)min(row0 + r, p.m - 1) * p.row_bytes + (size_t)u0 * UB;
+                                total += ((uint32_t)(src & 15) + seg + 15u) & ~15u;
+                            }
+                            mbar_expect_tx(&full[rp.s], total);
+                            for (uint32_t r = 0; r < 16; r++) {
+                                const size_t src = (size_t)min(row0 + r, p.m - 1) * p.row_bytes + (size_t)u0 * UB;
+                                const uint32_t skew = (uint32_t)(src & 15);
+                                bulk_g2s(dst + (size_t)r * L.rs, p.w + (src - skew), (skew + seg + 15u) & ~15u, &full[rp.s]);
+                            }
                         }
+                        OKF_GEMV_TRACE(1);
+                        rp.next(L.nstage);
                     }
                 }
             }
@@ -461,20 +490,20 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     }
 
     // ---- consumers
+    OKF_GEMV_TRACE(2);
     pdl_wait();  // activations come from the previous kernel; outputs may still be read by it
+    OKF_GEMV_TRACE(3);
 
     const uint32_t tid = threadIdx.x;  // 0 .. kConsumers - 1
-    uint32_t cphase = 0;
-    auto consumer_sync = [&]() -> bool {
-        __syncwarp();
+    // A wait that gives up marks the warp dead; a dead warp skips further waits but
+    // keeps walking the loops, so the barriers among the consumer warps still match.
+    bool alive = true;
+    auto wait_full = [&](uint32_t s, uint32_t use) {
         bool ok = true;
-        if (lane == 0) {
-            mbar_arrive(cbar);
-            ok = mbar_wait(cbar, cphase & 1, abort_flag, p.status, kStatusFullTimeout);
-        }
-        cphase++;
-        return __shfl_sync(0xffffffffu, ok, 0);
+        if (alive && lane == 0) ok = mbar_wait(&full[s], use & 1, abort_flag, p.status, kStatusFullTimeout);
+        alive = alive && __shfl_sync(0xffffffffu, ok, 0);
     };
+    auto consumer_sync = [&]() { named_bar_sync(1, kConsumers); };
 
     // Which effective column of x this thread feeds into the MMA (column g of B).
     // Threads with nothing to feed read a block of zeros laid out like a column,
@@ -492,64 +521,82 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     const uint32_t xs_ustride = x_active ? kXsUnit : 0;
     if (tid < kZeroBytes / 4) reinterpret_cast<uint32_t *>(zeros)[tid] = 0u;
 
-    uint32_t si = 0;
+    RingPos rp;
+    uint32_t rot = 0;  // the deal of units to warps rotates from step to step
     for (uint32_t gb = 0; gb < ntl; gb += L.group) {
         const uint32_t gn = min(L.group, ntl - gb);
         for (uint32_t i = tid; i < gn * kGemvWarps * 16 * L.nc; i += kConsumers) red[i] = 0.f;
         for (uint32_t j0 = 0; j0 < p.nchunk; j0 += L.panel) {
             const uint32_t j1 = min(j0 + L.panel, p.nchunk);
             const uint32_t pu0 = j0 * p.cb, pnu = min(j1 * p.cb, p.nunit) - pu0;
-            // the previous panel is still being read until every warp gets here
-            if ((gb > 0 || j0 > 0) && !consumer_sync()) return;
-            stage_x<TY, XDT>(xs, SEP ? xsum : nullptr, L, p.x, p.k, pu0, pnu, tid);
-            if (!consumer_sync()) return;
+            if (gb == 0 || L.panel < p.nchunk) {
+                // the previous panel is still being read until every warp gets here
+                if (gb > 0 || j0 > 0) consumer_sync();
+                stage_x<TY, XDT>(xs, SEP ? xsum : nullptr, L, p.x, p.k, pu0, pnu, tid);
+            }
+            consumer_sync();
+            OKF_GEMV_TRACE(4);
             for (uint32_t j = j0; j < j1; j++) {
                 const uint32_t u0 = j * p.cb, nu = min(p.cb, p.nunit - u0);
                 const uint32_t pu = u0 - pu0;  // first unit of the chunk inside the panel
-                for (uint32_t tl = gb; tl < gb + gn; tl++, si += spt) {
-                    // this warp's first unit in the chunk; the deal rotates from tile to tile
-                    uint32_t u = (warp + kGemvWarps - (si * p.cb) % kGemvWarps) % kGemvWarps;
-                    const uint32_t sA = si % L.nstage, sB = (si + spt - 1) % L.nstage;
-                    bool ok = true;
-                    if (lane == 0) {
-                        ok = mbar_wait(&full[sA], (si / L.nstage) & 1, abort_flag, p.status, kStatusFullTimeout);
-                        if (ok && spt == 2)
-                            ok = mbar_wait(&full[sB], ((si + 1) / L.nstage) & 1, abort_flag, p.status, kStatusFullTimeout);
+                // in whole-row stages a row holds every unit; in segment stages only this chunk's
+                const uint32_t ubase = L.mode == 2 ? 0 : u0;
+                for (uint32_t tl = gb; tl < gb + gn; tl += L.tps) {
+                    const uint32_t tn = min(L.tps, gb + gn - tl);
+                    const uint32_t sA = rp.s;
+                    OKF_GEMV_TRACE(5);
+                    wait_full(rp.s, rp.use);
+                    rp.next(L.nstage);
+                    const uint32_t sB = rp.s;
+                    if (spt == 2) {
+                        wait_full(rp.s, rp.use);
+                        rp.next(L.nstage);
                     }
-                    if (!__shfl_sync(0xffffffffu, ok, 0)) return;
-                    // rows g and g + 8 of the tile
+                    OKF_GEMV_TRACE(6);
+                    // rows g and g + 8 of the step's first tile
                     const uint8_t *ra = stages + (size_t)sA * L.stage_bytes + (size_t)g * L.rs;
                     const uint8_t *rb = L.mode == 1 ? stages + (size_t)sB * L.stage_bytes + (size_t)g * L.rs
                                                     : ra + (size_t)8 * L.rs;
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    const bool any = u < nu;
-                    for (; u < nu; u += kGemvWarps) {
-                        // in whole-row stages a row holds every unit; in segment stages only this chunk's
-                        const uint32_t uu = L.mode == 2 ? u : u0 + u;
-                        uint32_t xf[32];
-                        {
-                            const uint4 *xp = reinterpret_cast<const uint4 *>(xs_mine + (pu + u) * xs_ustride);
+                    if (L.mode == 2 && L.ragged) {  // skip what the copy fetched below each segment's start
+                        const uint32_t row = (t0 + tl) * 16 + g;
+                        ra += ((size_t)min(row, p.m - 1) * p.row_bytes + (size_t)u0 * UB) & 15;
+                        rb += ((size_t)min(row + 8, p.m - 1) * p.row_bytes + (size_t)u0 * UB) & 15;
+                    }
+                    const uint32_t tile_bytes = 16 * L.rs;
+                    // this warp's units: v = first, first + 8, ... of the step's tn * nu,
+                    // unit v being unit v % nu of tile v / nu
+                    const uint32_t total = tn * nu;
+                    uint32_t v = (warp + kGemvWarps - rot) & (kGemvWarps - 1);
+                    rot = (rot + total) & (kGemvWarps - 1);
+                    uint32_t ti = 0, u = v;
+                    while (u >= nu && ti < tn) { u -= nu; ti++; }
+                    while (v < total) {
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                        const uint32_t cur = ti;
+                        const uint8_t *ta = ra + (size_t)cur * tile_bytes, *tb = rb + (size_t)cur * tile_bytes;
+                        do {
+                            uint32_t xf[32];
+                            {
+                                const uint4 *xp = reinterpret_cast<const uint4 *>(xs_mine + (pu + u) * xs_ustride);
 #pragma unroll
-                            for (int q = 0; q < 8; q++) {
-                                const uint4 v = xp[q];
-                                xf[4 * q] = v.x; xf[4 * q + 1] = v.y; xf[4 * q + 2] = v.z; xf[4 * q + 3] = v.w;
+                                for (int q = 0; q < 8; q++) {
+                                    const uint4 w4 = xp[q];
+                                    xf[4 * q] = w4.x; xf[4 * q + 1] = w4.y; xf[4 * q + 2] = w4.z; xf[4 * q + 3] = w4.w;
+                                }
                             }
-                        }
-                        if constexpr (SEP) {
-                            const float4 xq = *reinterpret_cast<const float4 *>(xsum + ((pu + u) * 8 + 2 * c) * 2);
-                            unit_sep<TY>(ra + (size_t)uu * UB, rb + (size_t)uu * UB, c, xf, xq, grid, acc);
-                        } else {
-                            unit_q4k_pre(ra + (size_t)uu * UB, rb + (size_t)uu * UB, c, xf, acc);
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(&empty[sA]);
-                        if (spt == 2) mbar_arrive(&empty[sB]);
-                    }
-                    if (any) {
-                        // add into this warp's own slot of the partial-sum buffer
-                        float *dst = red + ((size_t)(tl - gb) * kGemvWarps + warp) * 16 * L.nc;
+                            const uint32_t off = (ubase + u) * UB;
+                            if constexpr (SEP) {
+                                const float4 xq = *reinterpret_cast<const float4 *>(xsum + ((pu + u) * 8 + 2 * c) * 2);
+                                unit_sep<TY>(ta + off, tb + off, c, xf, xq, grid, acc);
+                            } else {
+                                unit_q4k_pre(ta + off, tb + off, c, xf, acc);
+                            }
+                            v += kGemvWarps;
+                            u += kGemvWarps;
+                            while (u >= nu && v < total) { u -= nu; ti++; }
+                        } while (v < total && ti == cur);
+                        // add into this warp's own slot of the tile's partial sums
+                        float *dst = red + ((size_t)(tl - gb + cur) * kGemvWarps + warp) * 16 * L.nc;
                         if constexpr (SEP) {
                             // each thread of the quad covered another quarter: add them up
 #pragma unroll
@@ -582,11 +629,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                             }
                         }
                     }
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&empty[sA]);
+                        if (spt == 2) mbar_arrive(&empty[sB]);
+                    }
+                    OKF_GEMV_TRACE(7);
                 }
             }
         }
         // every warp's partials of this group are in: add them in warp order and store
-        if (!consumer_sync()) return;
+        consumer_sync();
         const uint32_t per_tile = 16 * L.nc;
         for (uint32_t i = tid; i < gn * per_tile; i += kConsumers) {
             const uint32_t tl = i / per_tile, r = (i % per_tile) / L.nc, col = i % L.nc;
@@ -597,8 +650,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
             const uint32_t row = (t0 + gb + tl) * 16 + r;
             if (row < p.m) p.out[(size_t)col * p.m + row] = sum;
         }
-        if (gb + L.group < ntl && !consumer_sync()) return;  // before the buffer is zeroed again
+        if (gb + L.group < ntl) consumer_sync();  // before the buffer is zeroed again
     }
+    OKF_GEMV_TRACE(8);
 }
 
 // Shared-memory plan.  Two CTAs share an SM (this kernel's and the next one's,
@@ -606,12 +660,14 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
 //
 // Ring stages.  A bulk copy costs the copy engine about 50 ns however small it
 // is, and a stage hand-over costs the producer a few hundred, so stages are
-// large (20 - 46 KB) and filled by as few copies as possible: when 16 (or 8)
-// whole rows fit in a stage they are one contiguous copy -- which also makes the
-// 2-byte-aligned layouts copyable, since 8 rows always start on a 16-byte
-// boundary -- otherwise rows are cut into segments of at least 2.4 KB, one copy
-// per row, which needs 16-byte aligned rows and segments.
-static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, GemvArgs &a, GemvLayout &L) {
+// large (20 - 46 KB) and filled by as few copies as possible: when whole rows fit,
+// a stage is up to four tiles (or half a tile) of consecutive rows and one
+// contiguous copy -- which also makes the 2-byte-aligned layouts copyable, since
+// 8 rows always start on a 16-byte boundary -- otherwise rows are cut into
+// segments of at least 2.4 KB, one copy per row, which needs 16-byte aligned rows
+// and segments.  `tiles_per_cta` is the most tiles any CTA of the launch gets.
+static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, uint32_t tiles_per_cta,
+                        GemvArgs &a, GemvLayout &L) {
     const uint32_t ub = ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
     L.nc = n;
     L.ecols = xdt == DT_F32 ? (sep ? 2 : 8) : n;
@@ -620,6 +676,7 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, G
     const uint32_t per_tile = kGemvWarps * 16 * n * 4;
     L.group = 8192 / per_tile;
     if (L.group < 1) L.group = 1;
+    if (L.group > tiles_per_cta) L.group = tiles_per_cta;
     const uint32_t red_bytes = L.group * per_tile;
     const uint32_t grid_bytes = ty == T_IQ2_XXS ? 2048 : 0;
     const uint32_t stage_cap = 46 * 1024;
@@ -627,16 +684,25 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, G
     // candidate plans, best first: 16 whole rows, 8 whole rows, then ever shorter row segments
     for (uint32_t plan = 0; plan < 2 + nunit; plan++) {
         uint32_t nchunk, cb, rs, stage;
-        if (plan == 0) { L.mode = 0; nchunk = 1; cb = nunit; rs = row_bytes; stage = (16 * rs + 15) & ~15u; }
-        else if (plan == 1) { L.mode = 1; nchunk = 1; cb = nunit; rs = row_bytes; stage = (8 * rs + 15) & ~15u; }
+        L.tps = 1;
+        L.ragged = 0;
+        if (plan == 0) {
+            L.mode = 0; nchunk = 1; cb = nunit; rs = row_bytes;
+            // several tiles per stage while they fit and the CTA still gets two steps
+            while (L.tps < 4 && (L.tps + 1) * 16 * rs <= stage_cap && (L.tps + 1) * 2 <= tiles_per_cta) L.tps++;
+            stage = (L.tps * 16 * rs + 15) & ~15u;
+        } else if (plan == 1) { L.mode = 1; nchunk = 1; cb = nunit; rs = row_bytes; stage = (8 * rs + 15) & ~15u; }
         else {
             L.mode = 2;
             nchunk = plan;  // 2, 3, ...
             cb = (nunit + nchunk - 1) / nchunk;
             if ((nunit + cb - 1) / cb != nchunk) continue;
-            if (row_bytes % 16 || (cb * ub) % 16) continue;  // segment copies must be 16-byte aligned
             const uint32_t seg = cb * ub;
-            rs = seg % 32 == 16 ? seg : seg + 16;  // rows g and g + 1 on different banks
+            L.ragged = (row_bytes % 16 || seg % 16) ? 1 : 0;
+            // Q4_K reads its blocks with 16-byte loads, and its rows are always aligned
+            if (L.ragged && ty != T_IQ2_XXS && ty != T_Q2_0) continue;
+            rs = L.ragged ? ((seg + 15 + 15) & ~15u) : seg;  // room for the skipped bytes and the round-up
+            if (rs % 32 != 16) rs += 16;                      // rows g and g + 1 on different banks
             stage = 16 * rs;
         }
         if (stage > stage_cap) continue;
@@ -656,6 +722,9 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, G
             nstage = min_stages;
             panel = (budget - small - min_stages * stage) / per_chunk;
         }
+        // no deeper than the steps a CTA takes
+        const uint32_t steps = ((tiles_per_cta + L.tps - 1) / L.tps) * nchunk * (L.mode == 1 ? 2 : 1);
+        if (nstage > steps) nstage = steps < min_stages ? min_stages : steps;
         if (nstage > kMaxStages) nstage = kMaxStages;
         if (L.mode == 1) nstage &= ~1u;  // a tile takes two stages
         L.nstage = nstage;
@@ -675,7 +744,8 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, G
 template <int TY, int XDT, bool SEP>
 static cudaError_t launch_t(GemvArgs a, cudaStream_t s, int sms, int dev) {
     GemvLayout L;
-    if (!gemv_layout(TY, a.nunit, a.n, XDT, SEP, a, L)) return cudaErrorInvalidConfiguration;
+    const uint32_t ctas = a.tiles < (uint32_t)sms ? a.tiles : (uint32_t)sms;
+    if (!gemv_layout(TY, a.nunit, a.n, XDT, SEP, (a.tiles + ctas - 1) / ctas, a, L)) return cudaErrorInvalidConfiguration;
     static bool attr_set[64] = {};  // the opt-in is per device
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
@@ -684,7 +754,7 @@ static cudaError_t launch_t(GemvArgs a, cudaStream_t s, int sms, int dev) {
         attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.tiles < (uint32_t)sms ? a.tiles : (uint32_t)sms);
+    cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kGemvThreads);
     cfg.dynamicSmemBytes = L.smem_bytes;
     cfg.stream = s;
@@ -714,14 +784,23 @@ static cudaError_t launch_ty(const GemvArgs &a, int xdt, bool sep, cudaStream_t 
     return cudaErrorInvalidValue;
 }
 
-bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n) {
+bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n,
+                         int sms) {
     if (ty != T_Q4_K && ty != T_Q8_0 && ty != T_Q2_0 && ty != T_IQ2_XXS) return false;
     if (n == 0 || n > 8 || m == 0) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
     if ((uintptr_t)w % 16 || (uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
     GemvArgs a = {};
     GemvLayout L;
-    return gemv_layout(ty, k / 256, xdt == DT_F32 ? 1 : (n < 2 ? n : 2), xdt, true, a, L);
+    const uint32_t tiles = (m + 15) / 16, ctas = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
+    // the widest pass takes the most shared memory; narrower ones then fit too
+    const uint32_t tpc = (tiles + ctas - 1) / ctas;
+    if (!gemv_layout(ty, k / 256, xdt == DT_F32 ? 1 : (n < 2 ? n : 2), xdt, true, tpc, a, L)) return false;
+    if (ty == T_Q4_K && n > (xdt == DT_F32 ? 1u : 2u)) {
+        const uint32_t pre = xdt == DT_F32 ? 4 : 8;
+        if (!gemv_layout(ty, k / 256, n < pre ? n : pre, xdt, false, tpc, a, L)) return false;
+    }
+    return true;
 }
 
 // One launch covers one or two effective columns (SEP) or, for Q4_K, up to eight

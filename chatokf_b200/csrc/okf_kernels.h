@@ -17,7 +17,8 @@ cudaError_t launch_gemm_simple(int ty, const uint8_t *w, uint32_t k, uint32_t m,
 // Tensor-core matvec for 1..8 activation columns (okf_gemv.cu).  `supported`
 // says whether the shape, alignment and element type are ones it takes; the
 // caller routes everything else to the simple kernel.
-bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n);
+bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n,
+                         int sms);
 cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
                              uint32_t n, float *out, int *status, cudaStream_t s, int sms, int dev,
                              uint64_t *launches);

@@ -72,8 +72,8 @@ def test_dequant_row_slice(ctx, ty):
 SHAPES = {
     GGUFType.Q8_0: [(2048, 2048), (96, 37), (32, 5)],
     GGUFType.Q4_K: [(2560, 512), (9728, 64), (256, 3)],
-    GGUFType.IQ2_XXS: [(5120, 256), (17408, 40), (256, 1)],
-    GGUFType.Q2_0: [(2048, 384), (6144, 130), (128, 9)],
+    GGUFType.IQ2_XXS: [(5120, 256), (17408, 40), (17408, 301), (256, 1)],
+    GGUFType.Q2_0: [(2048, 384), (6144, 130), (9728, 50), (128, 9)],
 }
 
 
