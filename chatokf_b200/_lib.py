@@ -35,6 +35,8 @@ SIGNATURES = {
     "okf_row_bytes": (_sz, [_ci, _sz]),
     "okf_gemv": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _vp, _vp]),
     "okf_gemm": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, _vp, _ci, _vp]),
+    "okf_parallel_begin": (_ci, [_vp]),
+    "okf_parallel_end": (_ci, [_vp]),
     "okf_gemm_tile": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, _vp, _ci, _vp]),
     "okf_gemm_noalloc": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, _vp, _ci, _vp]),
     "okf_dequant": (_ci, [_vp, _ci, _vp, _u64, _u64, _vp, _vp]),

@@ -39,6 +39,28 @@ int grow(okf_ctx *ctx, void **buf, size_t *have, size_t need) {
     return OKF_OK;
 }
 
+// Launch what a parallel region has collected.
+int par_flush(okf_ctx *ctx) {
+    const uint32_t cnt = ctx->par_count;
+    if (cnt == 0) return OKF_OK;
+    ctx->par_count = 0;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    cudaError_t e = cudaSuccess;
+    if (cnt > 1 && gemv_group_supported(ctx->par_type, ctx->par_k, cnt, ctx->par_m, ctx->par_w, ctx->par_x,
+                                        ctx->par_xdt, ctx->par_n, ctx->sms)) {
+        e = launch_gemv_group(ctx->par_type, cnt, ctx->par_w, ctx->par_m, ctx->par_out, ctx->par_k, ctx->par_x,
+                              ctx->par_xdt, ctx->par_n, ctx->dev_status, ctx->par_stream, ctx->sms, ctx->device,
+                              &ctx->launches);
+    } else {
+        for (uint32_t i = 0; i < cnt && e == cudaSuccess; i++)
+            e = launch_gemv_fast(ctx->par_type, ctx->par_w[i], ctx->par_k, ctx->par_m[i], ctx->par_x, ctx->par_xdt,
+                                 ctx->par_n, ctx->par_out[i], ctx->dev_status, ctx->par_stream, ctx->sms,
+                                 ctx->device, &ctx->launches);
+    }
+    return e == cudaSuccess ? OKF_OK : cuda_fail(ctx, e);
+}
+
 int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
                   const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream,
                   bool force_tile) {
@@ -53,6 +75,19 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
     if (n <= 8 && !force_tile && odt == DT_F32) {
         const bool simple = ctx->flags & OKF_FLAG_SIMPLE_KERNELS;
         if (!simple && gemv_fast_supported(ty, k, m, wp, x, xdt, n, ctx->sms)) {
+            if (ctx->par_open) {
+                // inside a parallel region: join the waiting matvecs if this one multiplies
+                // the same x, else send them off and start a new set
+                const bool joins = ctx->par_count > 0 && ctx->par_count < 4 && ctx->par_type == ty &&
+                                   ctx->par_k == k && ctx->par_x == x && ctx->par_xdt == xdt && ctx->par_n == n &&
+                                   ctx->par_stream == s;
+                if (!joins && (rc = par_flush(ctx))) return rc;
+                const uint32_t i = ctx->par_count++;
+                ctx->par_type = ty; ctx->par_k = k; ctx->par_x = x; ctx->par_xdt = xdt; ctx->par_n = n;
+                ctx->par_stream = s;
+                ctx->par_w[i] = wp; ctx->par_m[i] = m; ctx->par_out[i] = (float *)out;
+                return OKF_OK;
+            }
             e = launch_gemv_fast(ty, wp, k, m, x, xdt, n, (float *)out, ctx->dev_status, s, ctx->sms, ctx->device,
                                  &ctx->launches);
             if (e != cudaSuccess) return cuda_fail(ctx, e);
@@ -225,6 +260,19 @@ int okf_gemv(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32
 int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
              const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream) {
     return gemm_dispatch(ctx, type, w, woff, k, m, x, xdt, n, out, odt, stream, false);
+}
+
+int okf_parallel_begin(okf_ctx *ctx) {
+    if (!ctx || ctx->par_open) return OKF_E_ARG;
+    ctx->par_open = true;
+    ctx->par_count = 0;
+    return OKF_OK;
+}
+
+int okf_parallel_end(okf_ctx *ctx) {
+    if (!ctx || !ctx->par_open) return OKF_E_ARG;
+    ctx->par_open = false;
+    return par_flush(ctx);
 }
 
 int okf_gemm_tile(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,

@@ -9,19 +9,27 @@
 // tiles into a ring of shared-memory stages; when whole rows fit, a stage is a
 // few tiles (or half a tile) of consecutive rows and one contiguous bulk copy,
 // otherwise rows are cut into k-chunks and a stage takes one segment per row.
-// The eight consumer
-// warps deal the units of a stage among themselves, add what they computed
-// into their own slots of a partial-sum buffer, and after a group of tiles the
-// slots are summed in warp order and stored, so results do not depend on
-// timing.
+// The eight consumer warps deal the units of a stage among themselves, add what
+// they computed into their own slots of a partial-sum buffer, and after a group
+// of tiles the slots are summed in warp order and stored, so results do not
+// depend on timing.
 //
-// Column trick ("SEP", one or two effective columns).  MMA column g stands for
-// (quarter g / 2 of the unit, effective column g % 2).  Thread c of a quad owns
-// the k of quarter c and feeds x only into that quarter's columns, so the
-// accumulator a thread reads back is the raw integer sum over exactly the 64 k
-// whose block scales it decoded; scales, mins and biases are applied in fp32.
-// More columns than two are run as several passes over column pairs, except
-// for Q4_K, which has a single-pass variant ("PRE") for up to eight.
+// Activations.  Each 32-wide block of a column of x is reduced to 16-bit
+// integers with one fp32 scale, x ~ xs * q, |q| <= 32512 (round to nearest; the
+// step is 2^-15 of the block's largest magnitude), and q is split into two
+// signed bytes, q = 256 * hi + lo.  Every kernel here works on these values, so
+// one column gives the same result whatever the batch width.
+//
+// One column ("SEP", integer tensor cores).  Weights go into the MMA as the
+// bytes they are stored as (nibbles and 2-bit codes after one AND, Q8_0 and
+// the IQ2_XXS codebook untouched), x as the hi / lo bytes, mma.sync m16n8k32
+// with s32 accumulators: the sums are exact integers.  MMA column g stands for
+// (quarter g / 2 of the unit, byte g % 2 of x).  Thread c of a quad owns the k
+// of quarter c and feeds x only into that quarter's columns, so the accumulator
+// a thread reads back is the sum over exactly the 64 k whose block scales it
+// decoded; scales, mins and biases are applied in fp32.  More columns are run
+// as one pass per column, except for Q4_K, which has a variant for four
+// columns per pass ("PRE", fp16 tensor cores, x = hi + lo in fp16).
 #include "okf_gemv_mma.cuh"
 #include "okf_kernels.h"
 
@@ -42,18 +50,27 @@ struct GemvLayout {
     uint32_t ragged;       // mode 2: row segments do not start on 16-byte boundaries
     uint32_t group;        // tiles summed per barrier
     uint32_t nc;           // real activation columns of this pass
-    uint32_t ecols;        // effective (fp16) columns staged in shared memory
-    uint32_t lo_off;       // fp32 activations: effective column of the lo half of column 0
-    uint32_t es;           // bytes between effective columns of the x panel
+    uint32_t ecols;        // columns of the x panel in shared memory (SEP: hi, lo bytes; PRE: 4 hi + 4 lo)
+    uint32_t es;           // bytes between columns of the x panel
     uint32_t panel;        // k-chunks whose slice of x is staged together
-    uint32_t xs_off, xsum_off, red_off, zero_off, grid_off;  // byte offsets in dynamic shared memory
+    uint32_t xs_off, info_off, red_off, zero_off, tab_off;  // byte offsets in dynamic shared memory
     uint32_t smem_bytes;
 };
 
 constexpr uint32_t kBarBytes = 256;
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kConsumers = kGemvWarps * 32;
-constexpr uint32_t kZeroBytes = 3 * 144 + 64 + 128;  // a column's worth of zeros for idle MMA columns
+constexpr uint32_t kZeroBytes = 3 * 144 + 64 + 128;  // PRE: a column's worth of zeros for idle MMA columns
+// SEP x panel: per unit and byte column, the 64 bytes of quarter c start at
+// c * 80, so the eight lanes of a load that carry data (4 quarters x 2 byte
+// columns, column stride = 64 mod 128) touch eight different 16-byte bank groups
+constexpr uint32_t kXqQuarter = 80, kXqUnit = 4 * kXqQuarter;
+constexpr float kXqMax = 32512.f;  // 127 * 256: hi stays a signed byte after rounding
+
+__host__ __device__ inline uint32_t xq_col_stride(uint32_t units) {
+    const uint32_t raw = units * kXqUnit;
+    return raw + ((64u + 128u - raw % 128u) % 128u);
+}
 
 __device__ __forceinline__ uint4 lds128(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
 
@@ -83,64 +100,94 @@ __device__ __forceinline__ void q4k_scale_min(const uint4 &h, uint32_t c, uint32
         mn = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
     }
 }
+// The same for two rows at once: bytes {row a: 2c, 2c+1, row b: 2c, 2c+1}.
+__device__ __forceinline__ void q4k_scale_min2(const uint4 &ha, const uint4 &hb, uint32_t c, uint32_t &sc,
+                                               uint32_t &mn) {
+    const uint32_t sel = (c & 1) ? 0x7632u : 0x5410u;
+    const uint32_t a = __byte_perm(ha.y, hb.y, sel), b = __byte_perm(ha.z, hb.z, sel), e = __byte_perm(ha.w, hb.w, sel);
+    if (c < 2) {
+        sc = a & 0x3F3F3F3Fu;
+        mn = b & 0x3F3F3F3Fu;
+    } else {
+        sc = (e & 0x0F0F0F0Fu) | ((a >> 2) & 0x30303030u);
+        mn = ((e >> 4) & 0x0F0F0F0Fu) | ((b >> 2) & 0x30303030u);
+    }
+}
+
+// ---- integer MMA: D (16 x 8, s32) += A (16 x 32, bytes) * B (32 x 8, signed bytes) ----
+// Thread (g = lane / 4, c = lane % 4): a0 / a2 = row g, a1 / a3 = row g + 8, at
+// k-slots 4c..4c+3 (a0, a1, b0) and 16+4c..16+4c+3 (a2, a3, b1); b = column g;
+// d[0], d[1] = row g, columns 2c, 2c+1; d[2], d[3] = row g + 8.
+template <bool SIGNED_A>
+__device__ __forceinline__ void imma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                     uint32_t b1) {
+    if constexpr (SIGNED_A)
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// first of a chain: D = A * B
+template <bool SIGNED_A>
+__device__ __forceinline__ void imma0(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                      uint32_t b1) {
+    if constexpr (SIGNED_A)
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    else
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// sum over the hi and lo bytes of x: columns 2c (hi) and 2c+1 (lo) of one row
+__device__ __forceinline__ float join_hi_lo(int hi, int lo) { return (float)(hi * 256 + lo); }
 
 // ---- per-unit arithmetic, SEP -------------------------------------------------
-// ua / ub: the unit in rows g and g + 8.  xf: this thread's 32 fp16 pairs of x in
-// the order stage_x() writes them.  xq: sums of x over the two 32-wide halves of
-// the thread's quarter, {lo half col 0, col 1, hi half col 0, col 1}.
-// acc: rows g, g + 8 x effective columns 0, 1.
-//
-// Weights become exact integers in the low mantissa bits of fp16 (subnormals
-// v * 2^-24), which the tensor cores multiply and sum exactly in fp32.
+// ua / ub: the unit in rows g and g + 8.  xf: this thread's 64 bytes of x (its
+// quarter of the unit, the byte column its MMA column stands for; zeros in the
+// lanes that feed nothing).  xi: for the two 32-wide blocks of the quarter,
+// {xs of the first, xs of the second, sum of x over the first, over the second}.
+// tab: IQ2_XXS codebook (256 x 8 magnitudes) followed by the 128 sign masks.
+// acc: rows g and g + 8.
 template <int TY>
 __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, uint32_t c,
-                                         const uint32_t (&xf)[32], const float4 &xq,
-                                         const uint64_t *grid, float (&acc)[4]) {
-    float lo0[4] = {0.f, 0.f, 0.f, 0.f}, lo1[4] = {0.f, 0.f, 0.f, 0.f};  // first 32 k of the quarter
-    float hi0[4] = {0.f, 0.f, 0.f, 0.f}, hi1[4] = {0.f, 0.f, 0.f, 0.f};  // last 32 k
+                                         const uint32_t (&xf)[16], const float4 &xi, const uint2 *tab,
+                                         float (&acc)[2]) {
     if constexpr (TY == T_Q4_K) {
         // {f16 d; f16 dmin; u8 scales[12]; u8 qs[128]} (LLM/Quantize/KQuants.swift:104-125).
-        // Group c of qs (32 bytes): low nibbles = sub-block 2c, high = 2c+1.
+        // Group c of qs (32 bytes): low nibbles = sub-block 2c, high = 2c+1, both in k order.
+        // The high nibbles stay where they are (16 x the value); 1/16 goes into the scale.
         const uint4 ha = lds128(ua), hb = lds128(ub);
         const uint4 a0 = lds128(ua + 16 + 32 * c), a1 = lds128(ua + 32 + 32 * c);
         const uint4 b0 = lds128(ub + 16 + 32 * c), b1 = lds128(ub + 32 + 32 * c);
         const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
         const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const uint32_t ml = 0x0F0F0F0Fu, mh = 0xF0F0F0F0u;
+        int lo[4], hi[4];
+        imma0<false>(lo, wa[0] & ml, wb[0] & ml, wa[1] & ml, wb[1] & ml, xf[0], xf[1]);
+        imma0<false>(hi, wa[0] & mh, wb[0] & mh, wa[1] & mh, wb[1] & mh, xf[8], xf[9]);
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            {   // bytes (b0, b2) and (b1, b3) pair up; low nibble at mantissa bit 0, high at bit 4
-                const uint32_t ta = wa[i] >> 8, tb = wb[i] >> 8;
-                mma_f16(lo0, wa[i] & 0x000F000Fu, wb[i] & 0x000F000Fu, ta & 0x000F000Fu, tb & 0x000F000Fu,
-                        xf[2 * i], xf[2 * i + 1]);
-                mma_f16(hi0, wa[i] & 0x00F000F0u, wb[i] & 0x00F000F0u, ta & 0x00F000F0u, tb & 0x00F000F0u,
-                        xf[16 + 2 * i], xf[16 + 2 * i + 1]);
-            }
-            {
-                const uint32_t ta = wa[i + 1] >> 8, tb = wb[i + 1] >> 8;
-                mma_f16(lo1, wa[i + 1] & 0x000F000Fu, wb[i + 1] & 0x000F000Fu, ta & 0x000F000Fu, tb & 0x000F000Fu,
-                        xf[2 * i + 2], xf[2 * i + 3]);
-                mma_f16(hi1, wa[i + 1] & 0x00F000F0u, wb[i + 1] & 0x00F000F0u, ta & 0x00F000F0u, tb & 0x00F000F0u,
-                        xf[16 + 2 * i + 2], xf[16 + 2 * i + 3]);
-            }
+        for (int i = 1; i < 4; i++) {
+            imma<false>(lo, wa[2 * i] & ml, wb[2 * i] & ml, wa[2 * i + 1] & ml, wb[2 * i + 1] & ml, xf[2 * i], xf[2 * i + 1]);
+            imma<false>(hi, wa[2 * i] & mh, wb[2 * i] & mh, wa[2 * i + 1] & mh, wb[2 * i + 1] & mh, xf[8 + 2 * i],
+                        xf[9 + 2 * i]);
         }
-        uint32_t sca, mna, scb, mnb;
-        q4k_scale_min(ha, c, sca, mna);
-        q4k_scale_min(hb, c, scb, mnb);
+        uint32_t sc, mn;
+        q4k_scale_min2(ha, hb, c, sc, mn);
         const float da = f16bits(ha.x & 0xFFFF), dma = f16bits(ha.x >> 16);
         const float db = f16bits(hb.x & 0xFFFF), dmb = f16bits(hb.x >> 16);
-        // 2^24 and 2^20 undo the mantissa placement of the low and high nibbles
-        const float sa0 = da * 16777216.f * byte_to_f32(sca, 0), sa1 = da * 1048576.f * byte_to_f32(sca, 1);
-        const float sb0 = db * 16777216.f * byte_to_f32(scb, 0), sb1 = db * 1048576.f * byte_to_f32(scb, 1);
-        const float ma0 = dma * byte_to_f32(mna, 0), ma1 = dma * byte_to_f32(mna, 1);
-        const float mb0 = dmb * byte_to_f32(mnb, 0), mb1 = dmb * byte_to_f32(mnb, 1);
-        acc[0] += sa0 * (lo0[0] + lo1[0]) + sa1 * (hi0[0] + hi1[0]) - ma0 * xq.x - ma1 * xq.z;
-        acc[1] += sa0 * (lo0[1] + lo1[1]) + sa1 * (hi0[1] + hi1[1]) - ma0 * xq.y - ma1 * xq.w;
-        acc[2] += sb0 * (lo0[2] + lo1[2]) + sb1 * (hi0[2] + hi1[2]) - mb0 * xq.x - mb1 * xq.z;
-        acc[3] += sb0 * (lo0[3] + lo1[3]) + sb1 * (hi0[3] + hi1[3]) - mb0 * xq.y - mb1 * xq.w;
+        const float x0 = xi.x, x1 = xi.y * 0.0625f;
+        acc[0] += da * (byte_to_f32(sc, 0) * (x0 * join_hi_lo(lo[0], lo[1])) + byte_to_f32(sc, 1) * (x1 * join_hi_lo(hi[0], hi[1]))) -
+                  dma * (byte_to_f32(mn, 0) * xi.z + byte_to_f32(mn, 1) * xi.w);
+        acc[1] += db * (byte_to_f32(sc, 2) * (x0 * join_hi_lo(lo[2], lo[3])) + byte_to_f32(sc, 3) * (x1 * join_hi_lo(hi[2], hi[3]))) -
+                  dmb * (byte_to_f32(mn, 2) * xi.z + byte_to_f32(mn, 3) * xi.w);
     } else if constexpr (TY == T_Q8_0) {
         // eight blocks {f16 d; i8 q[32]} (LLM/Gemma/Gemma4Quant.swift:51-69); thread c
-        // takes blocks 2c and 2c+1.  q + 128 is an unsigned byte in the mantissa;
-        // the bias leaves again as 128 * sum(x).
+        // takes blocks 2c and 2c+1; the quants go into the MMA as they are.
         uint32_t wa[17], wb[17];
         lds_a2<17>(ua + 68 * c, wa);  // {d0, q0[32], d1, q1[32]} = 68 bytes, 2-byte aligned
         lds_a2<17>(ub + 68 * c, wb);
@@ -154,89 +201,85 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
             qa[8 + i] = wa[9 + i];
             qb[8 + i] = wb[9 + i];
         }
-        const uint32_t bias = 0x80808080u, m = 0x00FF00FFu;
+        int lo[4], hi[4];
+        imma0<true>(lo, qa[0], qb[0], qa[1], qb[1], xf[0], xf[1]);
+        imma0<true>(hi, qa[8], qb[8], qa[9], qb[9], xf[8], xf[9]);
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const uint32_t la = qa[i + h] ^ bias, lb = qb[i + h] ^ bias;
-                const uint32_t ha_ = qa[8 + i + h] ^ bias, hb_ = qb[8 + i + h] ^ bias;
-                mma_f16(h ? lo1 : lo0, la & m, lb & m, (la >> 8) & m, (lb >> 8) & m, xf[2 * (i + h)], xf[2 * (i + h) + 1]);
-                mma_f16(h ? hi1 : hi0, ha_ & m, hb_ & m, (ha_ >> 8) & m, (hb_ >> 8) & m, xf[16 + 2 * (i + h)],
-                        xf[16 + 2 * (i + h) + 1]);
-            }
+        for (int i = 1; i < 4; i++) {
+            imma<true>(lo, qa[2 * i], qb[2 * i], qa[2 * i + 1], qb[2 * i + 1], xf[2 * i], xf[2 * i + 1]);
+            imma<true>(hi, qa[8 + 2 * i], qb[8 + 2 * i], qa[9 + 2 * i], qb[9 + 2 * i], xf[8 + 2 * i], xf[9 + 2 * i]);
         }
         const float da0 = f16bits(wa[0] & 0xFFFF), da1 = f16bits(wa[8] >> 16);
         const float db0 = f16bits(wb[0] & 0xFFFF), db1 = f16bits(wb[8] >> 16);
-        const float s = 16777216.f;
-        acc[0] += da0 * (s * (lo0[0] + lo1[0]) - 128.f * xq.x) + da1 * (s * (hi0[0] + hi1[0]) - 128.f * xq.z);
-        acc[1] += da0 * (s * (lo0[1] + lo1[1]) - 128.f * xq.y) + da1 * (s * (hi0[1] + hi1[1]) - 128.f * xq.w);
-        acc[2] += db0 * (s * (lo0[2] + lo1[2]) - 128.f * xq.x) + db1 * (s * (hi0[2] + hi1[2]) - 128.f * xq.z);
-        acc[3] += db0 * (s * (lo0[3] + lo1[3]) - 128.f * xq.y) + db1 * (s * (hi0[3] + hi1[3]) - 128.f * xq.w);
+        acc[0] += da0 * (xi.x * join_hi_lo(lo[0], lo[1])) + da1 * (xi.y * join_hi_lo(hi[0], hi[1]));
+        acc[1] += db0 * (xi.x * join_hi_lo(lo[2], lo[3])) + db1 * (xi.y * join_hi_lo(hi[2], hi[3]));
     } else if constexpr (TY == T_Q2_0) {
         // two blocks {f16 d; u8 qs[32]} of 128 ternary codes, weight = (code - 1) * d
         // (LLM/Base/Quant.swift:2-25).  Thread c takes half (c & 1) of block c >> 1:
-        // 16 bytes = 64 codes.  A 2-bit code sits at mantissa bit p in {0,2,4,6,8};
-        // x was staged multiplied by 2^(4-p), so every product is code * x * 2^-20.
+        // 16 bytes = 64 codes; byte t holds k 4t .. 4t+3.  Masking code s of every
+        // byte of a word in place gives 4^s times the codes of k = s, 4+s, 8+s, 12+s
+        // (x is staged in that order); the factors are undone on the integer sums.
         const uint8_t *pa = ua + 34 * (c >> 1), *pb = ub + 34 * (c >> 1);
         uint32_t wa[4], wb[4];
         lds_a2<4>(pa + 2 + 16 * (c & 1), wa);
         lds_a2<4>(pb + 2 + 16 * (c & 1), wb);
-        const float da = f16bits(*reinterpret_cast<const uint16_t *>(pa));
-        const float db = f16bits(*reinterpret_cast<const uint16_t *>(pb));
+        const float da = f16bits(ld_u16(pa)), db = f16bits(ld_u16(pb));
+        float sum[2][2];  // [32-wide half][row], times 64
 #pragma unroll
-        for (int j = 0; j < 4; j++) {  // word j = 16 codes = k 16j .. 16j+15 of the quarter
-            const uint32_t va = wa[j], vb = wb[j], ta = va >> 10, tb = vb >> 10;
-            float(&c0)[4] = j < 2 ? lo0 : hi0;
-            float(&c1)[4] = j < 2 ? lo1 : hi1;
-            mma_f16(c0, va & 0x00030003u, vb & 0x00030003u, va & 0x000C000Cu, vb & 0x000C000Cu, xf[8 * j], xf[8 * j + 1]);
-            mma_f16(c1, va & 0x00300030u, vb & 0x00300030u, va & 0x00C000C0u, vb & 0x00C000C0u, xf[8 * j + 2], xf[8 * j + 3]);
-            mma_f16(c0, va & 0x03000300u, vb & 0x03000300u, ta & 0x00030003u, tb & 0x00030003u, xf[8 * j + 4], xf[8 * j + 5]);
-            mma_f16(c1, ta & 0x000C000Cu, tb & 0x000C000Cu, ta & 0x00300030u, tb & 0x00300030u, xf[8 * j + 6], xf[8 * j + 7]);
+        for (int sub = 0; sub < 2; sub++) {
+            int t[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int s = 0; s < 4; s++) {
+                const uint32_t m = 0x03030303u << (2 * s);
+                int d[4];
+                imma0<false>(d, wa[2 * sub] & m, wb[2 * sub] & m, wa[2 * sub + 1] & m, wb[2 * sub + 1] & m,
+                             xf[8 * sub + s], xf[8 * sub + 4 + s]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) t[e] = t[e] + d[e] * (64 >> (2 * s));
+            }
+            sum[sub][0] = join_hi_lo(t[0], t[1]);
+            sum[sub][1] = join_hi_lo(t[2], t[3]);
         }
-        const float s = 1048576.f;
-        acc[0] += da * (s * (lo0[0] + lo1[0] + hi0[0] + hi1[0]) - xq.x - xq.z);
-        acc[1] += da * (s * (lo0[1] + lo1[1] + hi0[1] + hi1[1]) - xq.y - xq.w);
-        acc[2] += db * (s * (lo0[2] + lo1[2] + hi0[2] + hi1[2]) - xq.x - xq.z);
-        acc[3] += db * (s * (lo0[3] + lo1[3] + hi0[3] + hi1[3]) - xq.y - xq.w);
+        const float s = 0.015625f;
+        acc[0] += da * (s * (xi.x * sum[0][0] + xi.y * sum[1][0]) - xi.z - xi.w);
+        acc[1] += db * (s * (xi.x * sum[0][1] + xi.y * sum[1][1]) - xi.z - xi.w);
     } else {
-        // IQ2_XXS {f16 d; 8 x (u32 a0: four grid indices, u32 a1: four 7-bit sign
+        // IQ2_XXS {f16 d; 8 x (u32 a0: four codebook indices, u32 a1: four 7-bit sign
         // indices + 4-bit scale)} (LLM/Quantize/IQ2XXS.swift:34-53).  Thread c takes
-        // sub-blocks 2c and 2c+1.  Magnitudes (8, 25, 43) go into the mantissa, the
-        // sign into the fp16 sign bit; db = d * (0.5 + s) * 0.25 is applied in fp32.
+        // sub-blocks 2c and 2c+1.  A codebook entry is eight magnitude bytes = the two
+        // A registers of one row; sum(sign * mag * x) = sum(mag * x) - 2 * sum over the
+        // negative positions, the second from the magnitudes ANDed with the sign's byte
+        // mask.  db = d * (0.5 + s) * 0.25 is applied in fp32.
         uint32_t wa[4], wb[4];
         lds_a2<4>(ua + 2 + 16 * c, wa);
         lds_a2<4>(ub + 2 + 16 * c, wb);
-        const float da = f16bits(*reinterpret_cast<const uint16_t *>(ua));
-        const float db = f16bits(*reinterpret_cast<const uint16_t *>(ub));
-        const uint32_t m = 0x00FF00FFu, sm = 0x80008000u;
+        const float da = f16bits(ld_u16(ua)), db = f16bits(ld_u16(ub));
+        const uint2 *sgn = tab + 256;
+        float sum[2][2];
 #pragma unroll
         for (int sb = 0; sb < 2; sb++) {
             const uint32_t a0a = wa[2 * sb], a1a = wa[2 * sb + 1], a0b = wb[2 * sb], a1b = wb[2 * sb + 1];
+            int pos[4], neg[4];
 #pragma unroll
             for (int l = 0; l < 4; l++) {
-                const uint64_t ea = grid[(a0a >> (8 * l)) & 0xFF], eb = grid[(a0b >> (8 * l)) & 0xFF];
-                // sign byte times 0x4001: bit i stays at i, bit i + 2 lands on bit i + 16
-                const uint32_t sa = iq2_signs((a1a >> (7 * l)) & 127u) * 0x4001u;
-                const uint32_t sb_ = iq2_signs((a1b >> (7 * l)) & 127u) * 0x4001u;
-                const uint32_t la = (uint32_t)ea, ha = (uint32_t)(ea >> 32), lb = (uint32_t)eb, hb = (uint32_t)(eb >> 32);
-                float(&cc)[4] = sb == 0 ? (l & 1 ? lo1 : lo0) : (l & 1 ? hi1 : hi0);
-                // registers hold magnitudes (0, 2), (1, 3) then (4, 6), (5, 7) with their signs
-                mma_f16(cc, (la & m) ^ ((sa << 15) & sm), (lb & m) ^ ((sb_ << 15) & sm),
-                        ((la >> 8) & m) ^ ((sa << 14) & sm), ((lb >> 8) & m) ^ ((sb_ << 14) & sm),
-                        xf[16 * sb + 4 * l], xf[16 * sb + 4 * l + 1]);
-                mma_f16(cc, (ha & m) ^ ((sa << 11) & sm), (hb & m) ^ ((sb_ << 11) & sm),
-                        ((ha >> 8) & m) ^ ((sa << 10) & sm), ((hb >> 8) & m) ^ ((sb_ << 10) & sm),
-                        xf[16 * sb + 4 * l + 2], xf[16 * sb + 4 * l + 3]);
+                const uint2 ea = tab[(a0a >> (8 * l)) & 0xFF], eb = tab[(a0b >> (8 * l)) & 0xFF];
+                const uint2 ma = sgn[(a1a >> (7 * l)) & 127u], mb = sgn[(a1b >> (7 * l)) & 127u];
+                const uint32_t x0 = xf[8 * sb + 2 * l], x1 = xf[8 * sb + 2 * l + 1];
+                if (l == 0) {
+                    imma0<false>(pos, ea.x, eb.x, ea.y, eb.y, x0, x1);
+                    imma0<false>(neg, ea.x & ma.x, eb.x & mb.x, ea.y & ma.y, eb.y & mb.y, x0, x1);
+                } else {
+                    imma<false>(pos, ea.x, eb.x, ea.y, eb.y, x0, x1);
+                    imma<false>(neg, ea.x & ma.x, eb.x & mb.x, ea.y & ma.y, eb.y & mb.y, x0, x1);
+                }
             }
+            sum[sb][0] = join_hi_lo(pos[0] - 2 * neg[0], pos[1] - 2 * neg[1]);
+            sum[sb][1] = join_hi_lo(pos[2] - 2 * neg[2], pos[3] - 2 * neg[3]);
         }
-        // db * 2^24 = d * (0.5 + s) * 2^22
-        const float sa0 = da * (0.5f + (float)(wa[1] >> 28)) * 4194304.f, sa1 = da * (0.5f + (float)(wa[3] >> 28)) * 4194304.f;
-        const float sb0 = db * (0.5f + (float)(wb[1] >> 28)) * 4194304.f, sb1 = db * (0.5f + (float)(wb[3] >> 28)) * 4194304.f;
-        acc[0] += sa0 * (lo0[0] + lo1[0]) + sa1 * (hi0[0] + hi1[0]);
-        acc[1] += sa0 * (lo0[1] + lo1[1]) + sa1 * (hi0[1] + hi1[1]);
-        acc[2] += sb0 * (lo0[2] + lo1[2]) + sb1 * (hi0[2] + hi1[2]);
-        acc[3] += sb0 * (lo0[3] + lo1[3]) + sb1 * (hi0[3] + hi1[3]);
+        const float sa0 = da * (0.5f + (float)(wa[1] >> 28)) * 0.25f, sa1 = da * (0.5f + (float)(wa[3] >> 28)) * 0.25f;
+        const float sb0 = db * (0.5f + (float)(wb[1] >> 28)) * 0.25f, sb1 = db * (0.5f + (float)(wb[3] >> 28)) * 0.25f;
+        acc[0] += sa0 * (xi.x * sum[0][0]) + sa1 * (xi.y * sum[1][0]);
+        acc[1] += sb0 * (xi.x * sum[0][1]) + sb1 * (xi.y * sum[1][1]);
     }
 }
 
@@ -280,98 +323,138 @@ __device__ __forceinline__ void unit_q4k_pre(const uint8_t *ua, const uint8_t *u
 }
 
 // ---- staging x ------------------------------------------------------------------
-// One item is 16 consecutive k of one real column: converted to fp16 (hi and lo
-// parts for fp32 input), re-ordered into the eight registers the unit code
-// expects, and summed; two neighbouring items make one 32-wide sum.
-//   Q4_K / Q8_0 / IQ2_XXS: register 2q + (j & 1) = (x[4q + j], x[4q + j + 2])
-//   Q2_0:                  register i = (x[i], x[i + 8]) * 2^(4 - p(i)), p = 0,2,4,6,8,0,2,4
-template <int TY, int XDT>
-__device__ __forceinline__ void stage_x(uint8_t *xs, float *xsum, const GemvLayout &L, const void *x,
-                                        uint32_t kdim, uint32_t u_first, uint32_t nu, uint32_t tid) {
-    const uint32_t items_per_col = nu * 16;
-    const uint32_t total = (L.nc * items_per_col + 31) & ~31u;  // whole warps, for the shuffles below
-    for (uint32_t i = tid; i < total; i += kConsumers) {
-        const bool live = i < L.nc * items_per_col;
-        const uint32_t col = live ? i / items_per_col : 0, it = live ? i % items_per_col : 0;
-        const uint32_t u = it >> 4, c = (it >> 2) & 3, q = it & 3;  // unit, quarter, 16-k piece of the quarter
-        const size_t src = (size_t)col * kdim + (size_t)(u_first + u) * 256 + c * 64 + q * 16;
-        float v[16];
-        if (live) {
-            if constexpr (XDT == DT_F32) {
-                const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + src);
+// One item is 16 consecutive k of one column; two neighbouring items (lanes)
+// make one 32-wide block and agree on its scale.  Returns the 16 integers, the
+// block's scale (NaN if the block holds a NaN, so that it spreads to the
+// results as it would in a plain dot product) and the block's integer sum.
+template <int XDT>
+__device__ __forceinline__ void quantize16(const void *x, size_t src, bool live, int (&q)[16], float &xs, int &qsum) {
+    float v[16];
+    if (live) {
+        if constexpr (XDT == DT_F32) {
+            const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + src);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float4 f = __ldg(p + j);
-                    v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
-                }
-            } else {
-                const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(x) + src);
+            for (int j = 0; j < 4; j++) {
+                const float4 f = __ldg(p + j);
+                v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
+            }
+        } else {
+            const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(x) + src);
 #pragma unroll
-                for (int j = 0; j < 2; j++) {
-                    const uint4 r = __ldg(p + j);
-                    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+            for (int j = 0; j < 2; j++) {
+                const uint4 r = __ldg(p + j);
+                const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        if constexpr (XDT == DT_F16) {
-                            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
-                            v[8 * j + 2 * e] = f.x; v[8 * j + 2 * e + 1] = f.y;
-                        } else {
-                            v[8 * j + 2 * e] = __uint_as_float(w[e] << 16);
-                            v[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-                        }
+                for (int e = 0; e < 4; e++) {
+                    if constexpr (XDT == DT_F16) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
+                        v[8 * j + 2 * e] = f.x; v[8 * j + 2 * e + 1] = f.y;
+                    } else {
+                        v[8 * j + 2 * e] = __uint_as_float(w[e] << 16);
+                        v[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
                     }
                 }
             }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; j++) v[j] = 0.f;
         }
-        float hi[16], lo[16], shi = 0.f, slo = 0.f;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = 0.f;
+    }
+    float amax = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        amax = fmaxf(amax, fabsf(v[j]));
+        bad = bad || v[j] != v[j];
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    bad = bad || __shfl_xor_sync(0xffffffffu, (int)bad, 1);
+    const float inv = amax > 0.f ? kXqMax / amax : 0.f;  // an infinite amax gives 0 and xs = inf
+    xs = bad ? __int_as_float(0x7FC00000) : amax / kXqMax;
+    qsum = 0;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        q[j] = __float2int_rn(v[j] * inv);
+        qsum += q[j];
+    }
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+}
+
+// SEP: one column as hi / lo bytes.  Byte order inside an item:
+//   Q4_K / Q8_0 / IQ2_XXS: k order
+//   Q2_0: register s = k (s, 4+s, 8+s, 12+s), the order the masked code words come in
+// info[unit * 4 + quarter] = {xs of its first block, of its second, sum of x over
+// the first, over the second}.
+template <int TY, int XDT>
+__device__ __forceinline__ void stage_x_bytes(uint8_t *xs, float4 *info, const GemvLayout &L, const void *x,
+                                              uint32_t u_first, uint32_t nu, uint32_t tid) {
+    const uint32_t items = nu * 16;
+    const uint32_t total = (items + 31) & ~31u;  // whole warps, for the shuffles
+    for (uint32_t i = tid; i < total; i += kConsumers) {
+        const bool live = i < items;
+        const uint32_t it = live ? i : 0;
+        const uint32_t u = it >> 4, c = (it >> 2) & 3, piece = it & 3;  // unit, quarter, 16-k piece of the quarter
+        int q[16], qsum;
+        float scale;
+        quantize16<XDT>(x, (size_t)(u_first + u) * 256 + c * 64 + piece * 16, live, q, scale, qsum);
+        if (!live) continue;
+        // q + 128 = 256 * hi + (lo + 128): hi is its byte 1, lo its byte 0 with the top bit flipped
+        uint32_t rh[4], rl[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            uint32_t t[4];
+#pragma unroll
+            for (int b = 0; b < 4; b++) t[b] = (uint32_t)(q[TY == T_Q2_0 ? 4 * b + r : 4 * r + b] + 128);
+            rh[r] = __byte_perm(__byte_perm(t[0], t[1], 0x0051), __byte_perm(t[2], t[3], 0x0051), 0x5410);
+            rl[r] = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410) ^ 0x80808080u;
+        }
+        uint8_t *dst = xs + u * kXqUnit + c * kXqQuarter + piece * 16;
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(rh[0], rh[1], rh[2], rh[3]);
+        *reinterpret_cast<uint4 *>(dst + L.es) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
+        if ((piece & 1) == 0) {
+            float *f = reinterpret_cast<float *>(info + u * 4 + c);
+            f[piece >> 1] = scale;
+            f[2 + (piece >> 1)] = scale * (float)qsum;
+        }
+    }
+}
+
+// PRE: up to four columns as fp16 pairs hi + lo of xs * q (columns j and 4 + j
+// of the panel), in the register order the unit code expects: register
+// 2r + (j & 1) of a 16-k item = (x[4r + j], x[4r + j + 2]).
+template <int XDT>
+__device__ __forceinline__ void stage_x_halves(uint8_t *xs, const GemvLayout &L, const void *x, uint32_t kdim,
+                                               uint32_t u_first, uint32_t nu, uint32_t tid) {
+    const uint32_t items_per_col = nu * 16;
+    const uint32_t total = (L.nc * items_per_col + 31) & ~31u;
+    for (uint32_t i = tid; i < total; i += kConsumers) {
+        const bool live = i < L.nc * items_per_col;
+        const uint32_t col = live ? i / items_per_col : 0, it = live ? i % items_per_col : 0;
+        const uint32_t u = it >> 4, c = (it >> 2) & 3, piece = it & 3;
+        int q[16], qsum;
+        float scale;
+        quantize16<XDT>(x, (size_t)col * kdim + (size_t)(u_first + u) * 256 + c * 64 + piece * 16, live, q, scale, qsum);
+        if (!live) continue;
+        float hi[16], lo[16];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            const float cl = fminf(fmaxf(v[j], -65504.f), 65504.f);
-            hi[j] = __half2float(__float2half_rn(cl));
-            lo[j] = cl - hi[j];
-            shi += hi[j];
-            slo += lo[j];
+            const float v = scale * (float)q[j];
+            hi[j] = __half2float(__float2half_rn(v));
+            lo[j] = v - hi[j];
         }
-        // 32-wide sums: items 2m and 2m + 1 sit in neighbouring lanes
-        shi += __shfl_xor_sync(0xffffffffu, shi, 1);
-        slo += __shfl_xor_sync(0xffffffffu, slo, 1);
-        if (!live) continue;
         uint32_t rh[8], rl[8];
 #pragma unroll
         for (int r = 0; r < 8; r++) {
-            int k0, k1;
-            float sc = 1.f;
-            if constexpr (TY == T_Q2_0) {
-                k0 = r; k1 = r + 8;
-                const int p = (r < 5 ? r : r - 5) * 2;
-                sc = p == 0 ? 16.f : p == 2 ? 4.f : p == 4 ? 1.f : p == 6 ? 0.25f : 0.0625f;
-            } else {
-                k0 = 4 * (r >> 1) + (r & 1); k1 = k0 + 2;
-            }
-            if constexpr (TY == T_Q2_0) {  // the scaled copy must stay finite in fp16
-                rh[r] = pack_h2(fminf(fmaxf(hi[k0] * sc, -65504.f), 65504.f), fminf(fmaxf(hi[k1] * sc, -65504.f), 65504.f));
-            } else {
-                rh[r] = pack_h2(hi[k0], hi[k1]);
-            }
-            rl[r] = pack_h2(lo[k0] * sc, lo[k1] * sc);
+            const int k0 = 4 * (r >> 1) + (r & 1), k1 = k0 + 2;
+            rh[r] = pack_h2(hi[k0], hi[k1]);
+            rl[r] = pack_h2(lo[k0], lo[k1]);
         }
-        uint8_t *dst = xs + col * L.es + u * kXsUnit + c * 144 + q * 32;
+        uint8_t *dst = xs + col * L.es + u * kXsUnit + c * 144 + piece * 32;
         *reinterpret_cast<uint4 *>(dst) = make_uint4(rh[0], rh[1], rh[2], rh[3]);
         *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(rh[4], rh[5], rh[6], rh[7]);
-        if constexpr (XDT == DT_F32) {
-            uint8_t *dl = dst + (size_t)L.lo_off * L.es;
-            *reinterpret_cast<uint4 *>(dl) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
-            *reinterpret_cast<uint4 *>(dl + 16) = make_uint4(rl[4], rl[5], rl[6], rl[7]);
-        }
-        if ((q & 1) == 0 && xsum) {
-            // xsum[(unit * 8 + sub-block) * 2 + effective column]; only the SEP layout uses it
-            float *s = xsum + ((size_t)u * 8 + c * 2 + (q >> 1)) * 2;
-            if constexpr (XDT == DT_F32) { s[0] = shi; s[1] = slo; }
-            else s[col] = shi;
-        }
+        uint8_t *dl = dst + (size_t)4 * L.es;
+        *reinterpret_cast<uint4 *>(dl) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
+        *reinterpret_cast<uint4 *>(dl + 16) = make_uint4(rl[4], rl[5], rl[6], rl[7]);
     }
 }
 
@@ -400,10 +483,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kMaxStages);
     uint8_t *stages = smem + kBarBytes;
     uint8_t *xs = smem + L.xs_off;
-    float *xsum = reinterpret_cast<float *>(smem + L.xsum_off);  // [unit][sub-block][2]
-    float *red = reinterpret_cast<float *>(smem + L.red_off);    // [tile in group][warp][16][nc]
+    float4 *info = reinterpret_cast<float4 *>(smem + L.info_off);  // SEP: [unit][quarter]
+    float *red = reinterpret_cast<float *>(smem + L.red_off);      // [tile in group][warp][16][nc]
     uint8_t *zeros = smem + L.zero_off;
-    const uint64_t *grid = reinterpret_cast<const uint64_t *>(smem + L.grid_off);
+    const uint2 *tab = reinterpret_cast<const uint2 *>(smem + L.tab_off);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const uint32_t t0 = (uint32_t)((uint64_t)p.tiles * blockIdx.x / gridDim.x);
@@ -422,8 +505,20 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if constexpr (TY == T_IQ2_XXS) {
-        uint64_t *gw = reinterpret_cast<uint64_t *>(smem + L.grid_off);
-        for (uint32_t i = threadIdx.x; i < 256; i += kGemvThreads) gw[i] = g_iq2xxs_grid[i];
+        // codebook, then for every 7-bit sign index the byte mask of its negative
+        // positions: bit j of idx | parity(idx) << 7 (LLM/Quantize/IQ2Grid.swift:73-85)
+        uint64_t *tw = reinterpret_cast<uint64_t *>(smem + L.tab_off);
+        for (uint32_t i = threadIdx.x; i < 256 + 128; i += kGemvThreads) {
+            if (i < 256) {
+                tw[i] = g_iq2xxs_grid[i];
+            } else {
+                const uint32_t sg = iq2_signs(i - 256);
+                uint64_t m = 0;
+                for (int j = 0; j < 8; j++)
+                    if ((sg >> j) & 1u) m |= 0xFFull << (8 * j);
+                tw[i] = m;
+            }
+        }
     }
     __syncthreads();
 
@@ -439,8 +534,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
             const uint32_t gn = min(L.group, ntl - gb);
             for (uint32_t j = 0; j < p.nchunk; j++) {
                 const uint32_t u0 = j * p.cb, nu = min(p.cb, p.nunit - u0);
-                for (uint32_t tl = gb; tl < gb + gn; tl += L.tps) {
-                    const uint32_t tn = min(L.tps, gb + gn - tl);
+                for (uint32_t tl = gb, tn; tl < gb + gn; tl += tn) {
+                    const GemvSeg sg = gemv_segment(p, t0 + tl);
+                    tn = min(min(L.tps, gb + gn - tl), sg.tile1 - (t0 + tl));  // a step stays inside one matrix
                     for (uint32_t half = 0; half < spt; half++, issued++) {
                         if (rp.use > 0 &&
                             !mbar_wait(&empty[rp.s], (rp.use - 1) & 1, abort_flag, p.status, kStatusEmptyTimeout)) {
@@ -453,16 +549,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                             }
                             return;
                         }
-                        const uint32_t row0 = (t0 + tl) * 16 + half * 8;
+                        const uint32_t row0 = (t0 + tl - sg.tile0) * 16 + half * 8;
                         uint8_t *dst = stages + (size_t)rp.s * L.stage_bytes;
                         if (L.mode != 2) {
                             // whole rows: one copy; the byte count is rounded up to 16, which may
                             // read a few bytes past the last row (weight buffers are padded)
                             const uint32_t want = L.mode == 1 ? 8u : 16u * tn;
-                            const uint32_t nrows = row0 < p.m ? min(want, p.m - row0) : 0u;
+                            const uint32_t nrows = row0 < sg.m ? min(want, sg.m - row0) : 0u;
                             const uint32_t bytes = (nrows * p.row_bytes + 15u) & ~15u;
                             mbar_expect_tx(&full[rp.s], bytes);
-                            if (bytes) bulk_g2s(dst, p.w + (size_t)row0 * p.row_bytes, bytes, &full[rp.s]);
+                            if (bytes) bulk_g2s(dst, sg.w + (size_t)row0 * p.row_bytes, bytes, &full[rp.s]);
                         } else {
                             // one copy per row segment.  A segment may start anywhere (2-byte
                             // aligned layouts): the copy starts at the 16-byte boundary below it
@@ -470,14 +566,14 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                             const uint32_t seg = nu * UB;
                             uint32_t total = 0;
                             for (uint32_t r = 0; r < 16; r++) {
-                                const size_t src = (size_t)min(row0 + r, p.m - 1) * p.row_bytes + (size_t)u0 * UB;
+                                const size_t src = (size_t)min(row0 + r, sg.m - 1) * p.row_bytes + (size_t)u0 * UB;
                                 total += ((uint32_t)(src & 15) + seg + 15u) & ~15u;
                             }
                             mbar_expect_tx(&full[rp.s], total);
                             for (uint32_t r = 0; r < 16; r++) {
-                                const size_t src = (size_t)min(row0 + r, p.m - 1) * p.row_bytes + (size_t)u0 * UB;
+                                const size_t src = (size_t)min(row0 + r, sg.m - 1) * p.row_bytes + (size_t)u0 * UB;
                                 const uint32_t skew = (uint32_t)(src & 15);
-                                bulk_g2s(dst + (size_t)r * L.rs, p.w + (src - skew), (skew + seg + 15u) & ~15u, &full[rp.s]);
+                                bulk_g2s(dst + (size_t)r * L.rs, sg.w + (src - skew), (skew + seg + 15u) & ~15u, &full[rp.s]);
                             }
                         }
                         OKF_GEMV_TRACE(1);
@@ -505,21 +601,23 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     };
     auto consumer_sync = [&]() { named_bar_sync(1, kConsumers); };
 
-    // Which effective column of x this thread feeds into the MMA (column g of B).
-    // Threads with nothing to feed read a block of zeros laid out like a column,
-    // so the inner loop has no divergence.
+    // What this thread feeds into column g of the MMA's B operand.
+    //   SEP: byte column g % 2 of x, and only in the lanes of quarter g / 2.
+    //   PRE: column g of the panel (hi halves of columns 0..3, then their lo halves);
+    //        threads with nothing to feed read a block of zeros laid out like a column.
     bool x_active;
-    uint32_t x_col;
+    const uint8_t *xs_mine;
+    uint32_t xs_ustride;
     if constexpr (SEP) {
-        x_col = g & 1;
-        x_active = (g >> 1) == c && x_col < L.ecols;
+        x_active = (g >> 1) == c;
+        xs_mine = xs + (g & 1) * L.es + c * kXqQuarter;
+        xs_ustride = kXqUnit;
     } else {
-        x_col = g;
-        x_active = XDT == DT_F32 ? (g & 3) < p.n : g < p.n;
+        x_active = (g & 3) < p.n;
+        xs_mine = x_active ? xs + g * L.es + c * 144 : zeros + c * 144 + (g & 1) * 64;
+        xs_ustride = x_active ? kXsUnit : 0;
+        if (tid < kZeroBytes / 4) reinterpret_cast<uint32_t *>(zeros)[tid] = 0u;
     }
-    const uint8_t *xs_mine = x_active ? xs + x_col * L.es + c * 144 : zeros + c * 144 + (g & 1) * 64;
-    const uint32_t xs_ustride = x_active ? kXsUnit : 0;
-    if (tid < kZeroBytes / 4) reinterpret_cast<uint32_t *>(zeros)[tid] = 0u;
 
     RingPos rp;
     uint32_t rot = 0;  // the deal of units to warps rotates from step to step
@@ -532,7 +630,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
             if (gb == 0 || L.panel < p.nchunk) {
                 // the previous panel is still being read until every warp gets here
                 if (gb > 0 || j0 > 0) consumer_sync();
-                stage_x<TY, XDT>(xs, SEP ? xsum : nullptr, L, p.x, p.k, pu0, pnu, tid);
+                if constexpr (SEP) stage_x_bytes<TY, XDT>(xs, info, L, p.x, pu0, pnu, tid);
+                else stage_x_halves<XDT>(xs, L, p.x, p.k, pu0, pnu, tid);
             }
             consumer_sync();
             OKF_GEMV_TRACE(4);
@@ -541,8 +640,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                 const uint32_t pu = u0 - pu0;  // first unit of the chunk inside the panel
                 // in whole-row stages a row holds every unit; in segment stages only this chunk's
                 const uint32_t ubase = L.mode == 2 ? 0 : u0;
-                for (uint32_t tl = gb; tl < gb + gn; tl += L.tps) {
-                    const uint32_t tn = min(L.tps, gb + gn - tl);
+                for (uint32_t tl = gb, tn; tl < gb + gn; tl += tn) {
+                    const GemvSeg sg = gemv_segment(p, t0 + tl);
+                    tn = min(min(L.tps, gb + gn - tl), sg.tile1 - (t0 + tl));
                     const uint32_t sA = rp.s;
                     OKF_GEMV_TRACE(5);
                     wait_full(rp.s, rp.use);
@@ -558,9 +658,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                     const uint8_t *rb = L.mode == 1 ? stages + (size_t)sB * L.stage_bytes + (size_t)g * L.rs
                                                     : ra + (size_t)8 * L.rs;
                     if (L.mode == 2 && L.ragged) {  // skip what the copy fetched below each segment's start
-                        const uint32_t row = (t0 + tl) * 16 + g;
-                        ra += ((size_t)min(row, p.m - 1) * p.row_bytes + (size_t)u0 * UB) & 15;
-                        rb += ((size_t)min(row + 8, p.m - 1) * p.row_bytes + (size_t)u0 * UB) & 15;
+                        const uint32_t row = (t0 + tl - sg.tile0) * 16 + g;
+                        ra += ((size_t)min(row, sg.m - 1) * p.row_bytes + (size_t)u0 * UB) & 15;
+                        rb += ((size_t)min(row + 8, sg.m - 1) * p.row_bytes + (size_t)u0 * UB) & 15;
                     }
                     const uint32_t tile_bytes = 16 * L.rs;
                     // this warp's units: v = first, first + 8, ... of the step's tn * nu,
@@ -571,57 +671,53 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                     uint32_t ti = 0, u = v;
                     while (u >= nu && ti < tn) { u -= nu; ti++; }
                     while (v < total) {
-                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
                         const uint32_t cur = ti;
                         const uint8_t *ta = ra + (size_t)cur * tile_bytes, *tb = rb + (size_t)cur * tile_bytes;
-                        do {
-                            uint32_t xf[32];
-                            {
+                        // this warp's own slot of the tile's partial sums
+                        float *dst = red + ((size_t)(tl - gb + cur) * kGemvWarps + warp) * 16 * L.nc;
+                        if constexpr (SEP) {
+                            float acc[2] = {0.f, 0.f};
+                            do {
+                                uint32_t xf[16];
+                                const uint4 *xp = reinterpret_cast<const uint4 *>(xs_mine + (pu + u) * xs_ustride);
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    uint4 w4 = make_uint4(0u, 0u, 0u, 0u);
+                                    if (x_active) w4 = xp[q];
+                                    xf[4 * q] = w4.x; xf[4 * q + 1] = w4.y; xf[4 * q + 2] = w4.z; xf[4 * q + 3] = w4.w;
+                                }
+                                const uint32_t off = (ubase + u) * UB;
+                                unit_sep<TY>(ta + off, tb + off, c, xf, info[(pu + u) * 4 + c], tab, acc);
+                                v += kGemvWarps;
+                                u += kGemvWarps;
+                                while (u >= nu && v < total) { u -= nu; ti++; }
+                            } while (v < total && ti == cur);
+                            // each thread of the quad covered another quarter: add them up
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+                            }
+                            if (c < 2) dst[g + 8 * c] += c ? acc[1] : acc[0];
+                        } else {
+                            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                            do {
+                                uint32_t xf[32];
                                 const uint4 *xp = reinterpret_cast<const uint4 *>(xs_mine + (pu + u) * xs_ustride);
 #pragma unroll
                                 for (int q = 0; q < 8; q++) {
                                     const uint4 w4 = xp[q];
                                     xf[4 * q] = w4.x; xf[4 * q + 1] = w4.y; xf[4 * q + 2] = w4.z; xf[4 * q + 3] = w4.w;
                                 }
-                            }
-                            const uint32_t off = (ubase + u) * UB;
-                            if constexpr (SEP) {
-                                const float4 xq = *reinterpret_cast<const float4 *>(xsum + ((pu + u) * 8 + 2 * c) * 2);
-                                unit_sep<TY>(ta + off, tb + off, c, xf, xq, grid, acc);
-                            } else {
+                                const uint32_t off = (ubase + u) * UB;
                                 unit_q4k_pre(ta + off, tb + off, c, xf, acc);
-                            }
-                            v += kGemvWarps;
-                            u += kGemvWarps;
-                            while (u >= nu && v < total) { u -= nu; ti++; }
-                        } while (v < total && ti == cur);
-                        // add into this warp's own slot of the tile's partial sums
-                        float *dst = red + ((size_t)(tl - gb + cur) * kGemvWarps + warp) * 16 * L.nc;
-                        if constexpr (SEP) {
-                            // each thread of the quad covered another quarter: add them up
+                                v += kGemvWarps;
+                                u += kGemvWarps;
+                                while (u >= nu && v < total) { u -= nu; ti++; }
+                            } while (v < total && ti == cur);
+                            // columns 4..7 hold the lo halves of columns 0..3
 #pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
-                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
-                            }
-                            if (c == 0) {
-                                if constexpr (XDT == DT_F32) {  // columns 0 / 1 are the hi / lo halves of x
-                                    dst[g] += acc[0] + acc[1];
-                                    dst[g + 8] += acc[2] + acc[3];
-                                } else {
-                                    dst[g * L.nc] += acc[0];
-                                    dst[(g + 8) * L.nc] += acc[2];
-                                    if (L.nc > 1) {
-                                        dst[g * L.nc + 1] += acc[1];
-                                        dst[(g + 8) * L.nc + 1] += acc[3];
-                                    }
-                                }
-                            }
-                        } else {
-                            if constexpr (XDT == DT_F32) {  // columns 4..7 hold the lo halves of columns 0..3
-#pragma unroll
-                                for (int e = 0; e < 4; e++) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
-                            }
+                            for (int e = 0; e < 4; e++) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
                                 const uint32_t col = 2 * c + (e & 1);
@@ -647,8 +743,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
             float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < kGemvWarps; w++) sum += src[(size_t)w * per_tile];
-            const uint32_t row = (t0 + gb + tl) * 16 + r;
-            if (row < p.m) p.out[(size_t)col * p.m + row] = sum;
+            const GemvSeg sg = gemv_segment(p, t0 + gb + tl);
+            const uint32_t row = (t0 + gb + tl - sg.tile0) * 16 + r;
+            if (row < sg.m) sg.out[(size_t)col * sg.m + row] = sum;
         }
         if (gb + L.group < ntl) consumer_sync();  // before the buffer is zeroed again
     }
@@ -666,35 +763,41 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
 // 8 rows always start on a 16-byte boundary -- otherwise rows are cut into
 // segments of at least 2.4 KB, one copy per row, which needs 16-byte aligned rows
 // and segments.  `tiles_per_cta` is the most tiles any CTA of the launch gets.
-static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, uint32_t tiles_per_cta,
-                        GemvArgs &a, GemvLayout &L) {
+static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, GemvArgs &a,
+                        GemvLayout &L) {
     const uint32_t ub = ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
-    L.nc = n;
-    L.ecols = xdt == DT_F32 ? (sep ? 2 : 8) : n;
-    L.lo_off = sep ? 1 : 4;
+    L.nc = sep ? 1 : n;
+    L.ecols = sep ? 2 : 8;
     const uint32_t budget = 112 * 1024;
-    const uint32_t per_tile = kGemvWarps * 16 * n * 4;
+    const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
     L.group = 8192 / per_tile;
     if (L.group < 1) L.group = 1;
     if (L.group > tiles_per_cta) L.group = tiles_per_cta;
     const uint32_t red_bytes = L.group * per_tile;
-    const uint32_t grid_bytes = ty == T_IQ2_XXS ? 2048 : 0;
+    const uint32_t tab_bytes = ty == T_IQ2_XXS ? (256 + 128) * 8 : 0;
     const uint32_t stage_cap = 46 * 1024;
     const uint32_t row_bytes = nunit * ub;
-    // candidate plans, best first: 16 whole rows, 8 whole rows, then ever shorter row segments
-    for (uint32_t plan = 0; plan < 2 + nunit; plan++) {
+    const uint32_t xunit = sep ? kXqUnit : kXsUnit, info_unit = sep ? 64 : 0;
+    // Candidate plans, best first: whole tiles, half tiles, then one copy per row of
+    // ever shorter segments (1, 2, ... per row).  Contiguous rows cannot be padded:
+    // when the row size is a multiple of 64 bytes the rows a warp reads together
+    // sit on the same banks, and per-row copies with a padded stride come first.
+    const bool same_banks = row_bytes % 64 == 0;
+    for (uint32_t plan = 0; plan < 3 + nunit; plan++) {
         uint32_t nchunk, cb, rs, stage;
         L.tps = 1;
         L.ragged = 0;
-        if (plan == 0) {
+        const uint32_t kind = same_banks ? (plan == 0 ? 2 : plan <= 2 ? plan - 1 : 2) : (plan < 2 ? plan : 2);
+        if (kind == 0) {
             L.mode = 0; nchunk = 1; cb = nunit; rs = row_bytes;
             // several tiles per stage while they fit and the CTA still gets two steps
             while (L.tps < 4 && (L.tps + 1) * 16 * rs <= stage_cap && (L.tps + 1) * 2 <= tiles_per_cta) L.tps++;
             stage = (L.tps * 16 * rs + 15) & ~15u;
-        } else if (plan == 1) { L.mode = 1; nchunk = 1; cb = nunit; rs = row_bytes; stage = (8 * rs + 15) & ~15u; }
+        } else if (kind == 1) { L.mode = 1; nchunk = 1; cb = nunit; rs = row_bytes; stage = (8 * rs + 15) & ~15u; }
         else {
             L.mode = 2;
-            nchunk = plan;  // 2, 3, ...
+            nchunk = same_banks ? (plan == 0 ? 1 : plan - 1) : plan - 1;  // 1, 2, 3, ...
+            if (same_banks && plan > 0 && nchunk == 1) continue;         // already tried
             cb = (nunit + nchunk - 1) / nchunk;
             if ((nunit + cb - 1) / cb != nchunk) continue;
             const uint32_t seg = cb * ub;
@@ -710,8 +813,8 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, u
         a.cb = cb;
         L.rs = rs;
         L.stage_bytes = stage;
-        const uint32_t per_chunk = L.ecols * cb * kXsUnit + cb * 8 * 2 * 4;  // x and its block sums
-        const uint32_t small = kBarBytes + red_bytes + kZeroBytes + grid_bytes + 64 + L.ecols * 128;
+        const uint32_t per_chunk = L.ecols * cb * xunit + cb * info_unit;  // x and what goes with it
+        const uint32_t small = kBarBytes + red_bytes + kZeroBytes + tab_bytes + 64 + L.ecols * 128;
         const uint32_t min_stages = L.mode == 1 ? 4 : 2;
         if (small + min_stages * stage + per_chunk > budget) continue;
         uint32_t nstage, panel;
@@ -729,13 +832,13 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, int xdt, bool sep, u
         if (L.mode == 1) nstage &= ~1u;  // a tile takes two stages
         L.nstage = nstage;
         L.panel = panel;
-        L.es = xs_col_stride(panel * cb);
+        L.es = sep ? xq_col_stride(panel * cb) : xs_col_stride(panel * cb);
         L.xs_off = kBarBytes + nstage * stage;
-        L.xsum_off = (L.xs_off + L.ecols * L.es + 15) & ~15u;
-        L.red_off = L.xsum_off + panel * cb * 8 * 2 * 4;
+        L.info_off = (L.xs_off + L.ecols * L.es + 15) & ~15u;
+        L.red_off = L.info_off + panel * cb * info_unit;
         L.zero_off = (L.red_off + red_bytes + 15) & ~15u;
-        L.grid_off = (L.zero_off + kZeroBytes + 15) & ~15u;
-        L.smem_bytes = L.grid_off + grid_bytes;
+        L.tab_off = (L.zero_off + kZeroBytes + 15) & ~15u;
+        L.smem_bytes = L.tab_off + tab_bytes;
         if (L.smem_bytes <= budget) return true;
     }
     return false;
@@ -745,7 +848,7 @@ template <int TY, int XDT, bool SEP>
 static cudaError_t launch_t(GemvArgs a, cudaStream_t s, int sms, int dev) {
     GemvLayout L;
     const uint32_t ctas = a.tiles < (uint32_t)sms ? a.tiles : (uint32_t)sms;
-    if (!gemv_layout(TY, a.nunit, a.n, XDT, SEP, (a.tiles + ctas - 1) / ctas, a, L)) return cudaErrorInvalidConfiguration;
+    if (!gemv_layout(TY, a.nunit, a.n, SEP, (a.tiles + ctas - 1) / ctas, a, L)) return cudaErrorInvalidConfiguration;
     static bool attr_set[64] = {};  // the opt-in is per device
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
@@ -784,45 +887,62 @@ static cudaError_t launch_ty(const GemvArgs &a, int xdt, bool sep, cudaStream_t 
     return cudaErrorInvalidValue;
 }
 
-bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n,
-                         int sms) {
+bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
+                          const void *x, int xdt, uint32_t n, int sms) {
     if (ty != T_Q4_K && ty != T_Q8_0 && ty != T_Q2_0 && ty != T_IQ2_XXS) return false;
-    if (n == 0 || n > 8 || m == 0) return false;
+    if (nseg == 0 || nseg > (uint32_t)kGemvSegs || n == 0 || n > 8) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
-    if ((uintptr_t)w % 16 || (uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
+    if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < nseg; i++) {
+        if (m[i] == 0 || (uintptr_t)w[i] % 16) return false;
+        tiles += (m[i] + 15) / 16;
+    }
     GemvArgs a = {};
     GemvLayout L;
-    const uint32_t tiles = (m + 15) / 16, ctas = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    // the widest pass takes the most shared memory; narrower ones then fit too
+    const uint32_t ctas = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
     const uint32_t tpc = (tiles + ctas - 1) / ctas;
-    if (!gemv_layout(ty, k / 256, xdt == DT_F32 ? 1 : (n < 2 ? n : 2), xdt, true, tpc, a, L)) return false;
-    if (ty == T_Q4_K && n > (xdt == DT_F32 ? 1u : 2u)) {
-        const uint32_t pre = xdt == DT_F32 ? 4 : 8;
-        if (!gemv_layout(ty, k / 256, n < pre ? n : pre, xdt, false, tpc, a, L)) return false;
-    }
+    if (!gemv_layout(ty, k / 256, 1, true, tpc, a, L)) return false;
+    if (ty == T_Q4_K && n > 1 && !gemv_layout(ty, k / 256, n < 4 ? n : 4, false, tpc, a, L)) return false;
     return true;
 }
 
-// One launch covers one or two effective columns (SEP) or, for Q4_K, up to eight
-// (PRE); wider requests are cut into passes over consecutive columns.
-cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
-                             uint32_t n, float *out, int *status, cudaStream_t s, int sms, int dev,
-                             uint64_t *launches) {
+bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n,
+                         int sms) {
+    const uint8_t *wp = (const uint8_t *)w;
+    return gemv_group_supported(ty, k, 1, &m, &wp, x, xdt, n, sms);
+}
+
+// One launch covers one column (SEP) or, for Q4_K, up to four (PRE); wider
+// requests are cut into passes over consecutive columns.  `nseg` matrices of the
+// same type and K share every launch.
+cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, const uint32_t *m, float *const *out,
+                              uint32_t k, const void *x, int xdt, uint32_t n, int *status, cudaStream_t s,
+                              int sms, int dev, uint64_t *launches) {
+    if (nseg == 0 || nseg > (uint32_t)kGemvSegs) return cudaErrorInvalidValue;
     GemvArgs a = {};
-    a.w = w; a.status = status; a.k = k; a.m = m;
+    a.status = status; a.k = k;
     a.nunit = k / 256;
-    a.tiles = (m + 15) / 16;
     a.row_bytes = a.nunit * (ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66);
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {
+        const uint32_t j = i < nseg ? i : nseg - 1;  // unused slots repeat the last one
+        a.w[i] = w[j];
+        a.m[i] = m[j];
+        if (i < nseg) tiles += (m[i] + 15) / 16;
+        a.tile_end[i] = tiles;
+    }
+    a.tiles = tiles;
     const size_t xsz = xdt == DT_F32 ? 4 : 2;
-    const uint32_t sep_cols = xdt == DT_F32 ? 1 : 2;                    // real columns per SEP pass
-    const uint32_t pre_cols = ty == T_Q4_K ? (xdt == DT_F32 ? 4 : 8) : 0;  // real columns per PRE pass
     for (uint32_t c0 = 0; c0 < n;) {
         const uint32_t left = n - c0;
-        const bool sep = left <= sep_cols || pre_cols == 0;
-        const uint32_t cap = sep ? sep_cols : pre_cols;
-        const uint32_t take = left < cap ? left : cap;
+        const bool sep = left == 1 || ty != T_Q4_K;
+        const uint32_t take = sep ? 1 : (left < 4 ? left : 4);
         a.x = (const uint8_t *)x + (size_t)c0 * k * xsz;
-        a.out = out + (size_t)c0 * m;
+        for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {
+            const uint32_t j = i < nseg ? i : nseg - 1;
+            a.out[i] = out[j] + (size_t)c0 * m[j];
+        }
         a.n = take;
         cudaError_t e;
         switch (ty) {
@@ -837,6 +957,12 @@ cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, c
         c0 += take;
     }
     return cudaSuccess;
+}
+
+cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
+                             uint32_t n, float *out, int *status, cudaStream_t s, int sms, int dev,
+                             uint64_t *launches) {
+    return launch_gemv_group(ty, 1, &w, &m, &out, k, x, xdt, n, status, s, sms, dev, launches);
 }
 
 }  // namespace okf

@@ -23,18 +23,37 @@
 
 namespace okf {
 
+// Up to kGemvSegs matrices of the same type and K that multiply the same x share
+// one launch: their tiles are numbered through, segment after segment.
+constexpr int kGemvSegs = 4;
 struct GemvArgs {
-    const uint8_t *w;
+    const uint8_t *w[kGemvSegs];
+    float *out[kGemvSegs];
+    uint32_t m[kGemvSegs];
+    uint32_t tile_end[kGemvSegs];  // running total of ceil(m / 16)
     const void *x;
-    float *out;
     int *status;     // device status word: 0 = ok, else a wait gave up (see kStatus*)
-    uint32_t k, m, n;
+    uint32_t k, n;
     uint32_t nunit;  // 256-wide units per row
-    uint32_t tiles;  // ceil(m / 16)
+    uint32_t tiles;  // all segments together
     uint32_t cb;     // units per chunk (one ring stage holds 16 rows x cb units)
     uint32_t nchunk; // chunks per tile
     uint32_t row_bytes;
 };
+
+// The segment a tile belongs to.
+struct GemvSeg {
+    const uint8_t *w;
+    float *out;
+    uint32_t m, tile0, tile1;
+};
+__device__ __forceinline__ GemvSeg gemv_segment(const GemvArgs &p, uint32_t tile) {
+    GemvSeg s = {p.w[0], p.out[0], p.m[0], 0u, p.tile_end[0]};
+#pragma unroll
+    for (int i = 1; i < kGemvSegs; i++)
+        if (tile >= p.tile_end[i - 1]) s = {p.w[i], p.out[i], p.m[i], p.tile_end[i - 1], p.tile_end[i]};
+    return s;
+}
 
 constexpr int kGemvWarps = 8;                      // consumer warps
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;  // + one producer warp

@@ -31,6 +31,17 @@ struct okf_ctx {
     // staged faults (host side only)
     double fault_rate;
     uint64_t fault_state;
+    // okf_parallel_begin .. okf_parallel_end: narrow matvecs of one x, type and K
+    // wait here and leave as one launch
+    bool par_open;
+    uint32_t par_count;
+    int par_type, par_xdt;
+    uint32_t par_k, par_n;
+    const void *par_x;
+    cudaStream_t par_stream;
+    const uint8_t *par_w[4];
+    uint32_t par_m[4];
+    float *par_out[4];
 };
 
 

@@ -22,6 +22,13 @@ bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const vo
 cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
                              uint32_t n, float *out, int *status, cudaStream_t s, int sms, int dev,
                              uint64_t *launches);
+// The same for up to four matrices of one type and K that multiply the same x:
+// one launch (per pass over columns) covers them all.
+bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
+                          const void *x, int xdt, uint32_t n, int sms);
+cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, const uint32_t *m, float *const *out,
+                              uint32_t k, const void *x, int xdt, uint32_t n, int *status, cudaStream_t s,
+                              int sms, int dev, uint64_t *launches);
 
 // Prefill matmul on tcgen05 / tensor memory (okf_gemm_tc.cu), any N.
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n);

@@ -9,6 +9,8 @@ libokfcuda.so.
 """
 from __future__ import annotations
 
+import contextlib
+
 import ctypes
 from dataclasses import dataclass
 
@@ -162,6 +164,17 @@ class CudaEnc:
     def gemm(self, w: GGUFTensor, X: torch.Tensor, out: torch.Tensor, off: Weights, N: int):
         """MetalEnc.gemm(w, X:, out:, off:, N:): out[n*M + m]."""
         self._gemm(self.ctx.lib.okf_gemm, "okf_gemm", w, X, out, off, N)
+
+    @contextlib.contextmanager
+    def parallel(self):
+        """MetalEnc.parallel { ... } (LLM/Base/MetalEnc.swift:42-47): the calls inside
+        have no order among themselves; narrow matvecs of the same x leave as one launch."""
+        c = self.ctx
+        c._check(c.lib.okf_parallel_begin(c.h), "okf_parallel_begin")
+        try:
+            yield self
+        finally:
+            c._check(c.lib.okf_parallel_end(c.h), "okf_parallel_end")
 
     def gemmTile(self, w: GGUFTensor, X: torch.Tensor, out: torch.Tensor, off: Weights, N: int):
         """MetalEnc.gemmTile: the tensor-core tile at any N (kernel bench)."""

@@ -109,6 +109,18 @@ OKF_API int okf_gemv(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff
 OKF_API int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
              const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream);
 
+/* Calls between begin and end have no order among themselves: the reference's
+ * MetalEnc.parallel { ... } (Base/MetalEnc.swift:42-47), which the engines wrap
+ * around gate || up and q || k || v (Qwen/QwenMetalEngine.swift:464-469, :691-696).
+ * Inside a region, okf_gemv / okf_gemm calls with N <= 8 that multiply the same
+ * x by matrices of one type and K (up to four) are held back and leave as ONE
+ * kernel launch, at okf_parallel_end or as soon as a call does not fit the set;
+ * every other call runs at once, as outside a region.  A launch error of a
+ * held-back call is returned by the call that sends the set off.  Regions do
+ * not nest.  Outputs of the region must not alias its inputs. */
+OKF_API int okf_parallel_begin(okf_ctx *ctx);
+OKF_API int okf_parallel_end(okf_ctx *ctx);
+
 /* Same contract as okf_gemm but always the tensor-core tile, whatever N is.
  * Replaces MetalEnc.gemmTile (Base/MetalEnc.swift:326-352), which the
  * reference's kernel bench uses to time the tile at small N. */

@@ -137,6 +137,55 @@ def test_narrow_gemm_vs_gemv(ctx, ty, n):
     assert rel_err(out.cpu().numpy(), oracle.matmul(ty, blocks, k, m, X, n)) <= GEMV_TIGHT
 
 
+@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("n", [1, 3])
+def test_parallel_region_matches_separate_calls(ctx, ty, n):
+    """Matvecs of one x inside a parallel region (the reference wraps gate || up
+    and q || k || v in MetalEnc.parallel, QwenMetalEngine.swift:464-469, :691-696)
+    leave as one launch and give bit-identical results to separate calls."""
+    k = SHAPES[ty][0][0]
+    ms = [200, 96, 513]
+    enc = CudaEnc(ctx)
+    X = dev(np.stack([lcg_fill(k, 5 + c) for c in range(n)]))
+    ws = [ctx.upload(make_weights(ty, m, k, seed=m)) for m in ms]
+    ts = [GGUFTensor(f"w{m}", (k, m), ty) for m in ms]
+    want = [torch.empty(n, m, dtype=torch.float32, device="cuda") for m in ms]
+    got = [torch.full((n, m), float("nan"), dtype=torch.float32, device="cuda") for m in ms]
+    for t, w, o in zip(ts, ws, want):
+        enc.gemm(t, X, o, w, n)
+    before = ctx.launches
+    with enc.parallel():
+        for t, w, o in zip(ts, ws, got):
+            enc.gemm(t, X, o, w, n)
+    passes = 1 if (n == 1 or ty == GGUFType.Q4_K) else n
+    assert ctx.launches - before == passes
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
+def test_parallel_region_mixed_calls(ctx):
+    """Calls that do not fit the waiting set (another x, another type) send it off
+    and still run; an unmatched end is an error."""
+    enc = CudaEnc(ctx)
+    k = 512
+    x1 = dev(lcg_fill(k, 1)); x2 = dev(lcg_fill(k, 2))
+    wa = make_weights(GGUFType.Q4_K, 64, k, seed=1); wb = make_weights(GGUFType.Q8_0, 48, k, seed=2)
+    ta, tb = GGUFTensor("a", (k, 64), GGUFType.Q4_K), GGUFTensor("b", (k, 48), GGUFType.Q8_0)
+    ua, ub = ctx.upload(wa), ctx.upload(wb)
+    outs = [torch.empty(m, dtype=torch.float32, device="cuda") for m in (64, 64, 48)]
+    with enc.parallel():
+        enc.gemv(ta, x1, outs[0], ua)
+        enc.gemv(ta, x2, outs[1], ua)
+        enc.gemv(tb, x2, outs[2], ub)
+    torch.cuda.synchronize()
+    for o, (ty, blocks, m, x) in zip(outs, [(GGUFType.Q4_K, wa, 64, x1), (GGUFType.Q4_K, wa, 64, x2),
+                                          (GGUFType.Q8_0, wb, 48, x2)]):
+        assert rel_err(o.cpu().numpy(), oracle.matvec(ty, blocks, k, m, x.cpu().numpy())) <= GEMV_TIGHT
+    with pytest.raises(OkfError):
+        ctx._check(ctx.lib.okf_parallel_end(ctx.h), "okf_parallel_end")
+
+
 # ---- matmul ------------------------------------------------------------------
 
 @pytest.mark.parametrize("ty", ALL_TYPES)
