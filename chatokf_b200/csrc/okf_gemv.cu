@@ -61,15 +61,19 @@ constexpr uint32_t kBarBytes = 256;
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kConsumers = kGemvWarps * 32;
 constexpr uint32_t kZeroBytes = 3 * 144 + 64 + 128;  // PRE: a column's worth of zeros for idle MMA columns
-// SEP x panel: per unit and byte column, the 64 bytes of quarter c start at
-// c * 80, so the eight lanes of a load that carry data (4 quarters x 2 byte
-// columns, column stride = 64 mod 128) touch eight different 16-byte bank groups
-constexpr uint32_t kXqQuarter = 80, kXqUnit = 4 * kXqQuarter;
+// SEP x panel: a unit of a byte column is its 256 bytes in k order, except that
+// in quarters 2 and 3 neighbouring 16-byte pieces are swapped; with the second
+// byte column 32 (mod 128) bytes after the first, the eight lanes of a load that
+// carry data (4 quarters x 2 byte columns) touch eight different bank groups.
+constexpr uint32_t kXqUnit = 256;
 constexpr float kXqMax = 32512.f;  // 127 * 256: hi stays a signed byte after rounding
 
 __host__ __device__ inline uint32_t xq_col_stride(uint32_t units) {
     const uint32_t raw = units * kXqUnit;
-    return raw + ((64u + 128u - raw % 128u) % 128u);
+    return raw + ((32u + 128u - raw % 128u) % 128u);
+}
+__host__ __device__ inline uint32_t xq_piece_offset(uint32_t c, uint32_t piece) {
+    return c * 64 + ((piece ^ (c >> 1)) & 3u) * 16;
 }
 
 __device__ __forceinline__ uint4 lds128(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
@@ -324,59 +328,73 @@ __device__ __forceinline__ void unit_q4k_pre(const uint8_t *ua, const uint8_t *u
 
 // ---- staging x ------------------------------------------------------------------
 // One item is 16 consecutive k of one column; two neighbouring items (lanes)
-// make one 32-wide block and agree on its scale.  Returns the 16 integers, the
-// block's scale (NaN if the block holds a NaN, so that it spreads to the
-// results as it would in a plain dot product) and the block's integer sum.
+// make one 32-wide block and agree on its scale.
+template <int XDT> struct XRaw { uint4 v[XDT == DT_F32 ? 4 : 2]; };
+
 template <int XDT>
-__device__ __forceinline__ void quantize16(const void *x, size_t src, bool live, int (&q)[16], float &xs, int &qsum) {
+__device__ __forceinline__ XRaw<XDT> load16(const void *x, size_t src, bool live) {
+    XRaw<XDT> r;
+    constexpr int NV = XDT == DT_F32 ? 4 : 2;
+    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(x) + src * (XDT == DT_F32 ? 4 : 2));
+#pragma unroll
+    for (int j = 0; j < NV; j++) r.v[j] = live ? __ldg(p + j) : make_uint4(0u, 0u, 0u, 0u);
+    return r;
+}
+
+// The 16 integers, the block's scale (NaN if the block holds a NaN, so that it
+// spreads to the results as it would in a plain dot product) and the block's
+// integer sum.
+template <int XDT>
+__device__ __forceinline__ void quantize16(const XRaw<XDT> &raw, int (&q)[16], float &xs, int &qsum) {
     float v[16];
-    if (live) {
-        if constexpr (XDT == DT_F32) {
-            const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + src);
+    if constexpr (XDT == DT_F32) {
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float4 f = __ldg(p + j);
-                v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
-            }
-        } else {
-            const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(x) + src);
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const uint4 r = __ldg(p + j);
-                const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    if constexpr (XDT == DT_F16) {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
-                        v[8 * j + 2 * e] = f.x; v[8 * j + 2 * e + 1] = f.y;
-                    } else {
-                        v[8 * j + 2 * e] = __uint_as_float(w[e] << 16);
-                        v[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-                    }
-                }
-            }
+        for (int j = 0; j < 4; j++) {
+            v[4 * j] = __uint_as_float(raw.v[j].x); v[4 * j + 1] = __uint_as_float(raw.v[j].y);
+            v[4 * j + 2] = __uint_as_float(raw.v[j].z); v[4 * j + 3] = __uint_as_float(raw.v[j].w);
         }
     } else {
 #pragma unroll
-        for (int j = 0; j < 16; j++) v[j] = 0.f;
-    }
-    float amax = 0.f;
-    bool bad = false;
+        for (int j = 0; j < 2; j++) {
+            const uint32_t w[4] = {raw.v[j].x, raw.v[j].y, raw.v[j].z, raw.v[j].w};
 #pragma unroll
-    for (int j = 0; j < 16; j++) {
-        amax = fmaxf(amax, fabsf(v[j]));
-        bad = bad || v[j] != v[j];
+            for (int e = 0; e < 4; e++) {
+                if constexpr (XDT == DT_F16) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
+                    v[8 * j + 2 * e] = f.x; v[8 * j + 2 * e + 1] = f.y;
+                } else {
+                    v[8 * j + 2 * e] = __uint_as_float(w[e] << 16);
+                    v[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+                }
+            }
+        }
     }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    bad = bad || __shfl_xor_sync(0xffffffffu, (int)bad, 1);
-    const float inv = amax > 0.f ? kXqMax / amax : 0.f;  // an infinite amax gives 0 and xs = inf
-    xs = bad ? __int_as_float(0x7FC00000) : amax / kXqMax;
-    qsum = 0;
+    // largest magnitude; a NaN anywhere makes the sum of squares-free test below fail
+    float m8[8], bad8[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        m8[j] = fmaxf(fabsf(v[j]), fabsf(v[j + 8]));
+        bad8[j] = v[j] + v[j + 8];  // NaN if either is (inf - inf cannot occur: same-block infs give NaN results anyway)
+    }
+#pragma unroll
+    for (int w = 4; w >= 1; w >>= 1)
+#pragma unroll
+        for (int j = 0; j < w; j++) {
+            m8[j] = fmaxf(m8[j], m8[j + w]);
+            bad8[j] = bad8[j] + bad8[j + w];
+        }
+    float amax = fmaxf(m8[0], __shfl_xor_sync(0xffffffffu, m8[0], 1));
+    const float nanprobe = bad8[0] + __shfl_xor_sync(0xffffffffu, bad8[0], 1);
+    const bool bad = nanprobe != nanprobe && !(amax == __int_as_float(0x7F800000));
+    const float inv = amax > 0.f ? __fdividef(kXqMax, amax) : 0.f;  // an infinite amax gives 0 and xs = inf
+    xs = bad ? __int_as_float(0x7FC00000) : amax * (1.f / kXqMax);
+    int s4[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int j = 0; j < 16; j++) {
         q[j] = __float2int_rn(v[j] * inv);
-        qsum += q[j];
+        s4[j & 3] += q[j];
     }
+    qsum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
     qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
 }
 
@@ -390,31 +408,41 @@ __device__ __forceinline__ void stage_x_bytes(uint8_t *xs, float4 *info, const G
                                               uint32_t u_first, uint32_t nu, uint32_t tid) {
     const uint32_t items = nu * 16;
     const uint32_t total = (items + 31) & ~31u;  // whole warps, for the shuffles
-    for (uint32_t i = tid; i < total; i += kConsumers) {
-        const bool live = i < items;
-        const uint32_t it = live ? i : 0;
-        const uint32_t u = it >> 4, c = (it >> 2) & 3, piece = it & 3;  // unit, quarter, 16-k piece of the quarter
-        int q[16], qsum;
-        float scale;
-        quantize16<XDT>(x, (size_t)(u_first + u) * 256 + c * 64 + piece * 16, live, q, scale, qsum);
-        if (!live) continue;
-        // q + 128 = 256 * hi + (lo + 128): hi is its byte 1, lo its byte 0 with the top bit flipped
-        uint32_t rh[4], rl[4];
+    constexpr uint32_t kFlight = 3;              // items a thread has in flight: the loads go out first
+    for (uint32_t base = tid; base < total; base += kFlight * kConsumers) {
+        XRaw<XDT> raw[kFlight];
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            uint32_t t[4];
-#pragma unroll
-            for (int b = 0; b < 4; b++) t[b] = (uint32_t)(q[TY == T_Q2_0 ? 4 * b + r : 4 * r + b] + 128);
-            rh[r] = __byte_perm(__byte_perm(t[0], t[1], 0x0051), __byte_perm(t[2], t[3], 0x0051), 0x5410);
-            rl[r] = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410) ^ 0x80808080u;
+        for (uint32_t r = 0; r < kFlight; r++) {
+            const uint32_t i = base + r * kConsumers;
+            raw[r] = load16<XDT>(x, (size_t)u_first * 256 + (size_t)i * 16, i < items);
         }
-        uint8_t *dst = xs + u * kXqUnit + c * kXqQuarter + piece * 16;
-        *reinterpret_cast<uint4 *>(dst) = make_uint4(rh[0], rh[1], rh[2], rh[3]);
-        *reinterpret_cast<uint4 *>(dst + L.es) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
-        if ((piece & 1) == 0) {
-            float *f = reinterpret_cast<float *>(info + u * 4 + c);
-            f[piece >> 1] = scale;
-            f[2 + (piece >> 1)] = scale * (float)qsum;
+#pragma unroll
+        for (uint32_t r = 0; r < kFlight; r++) {
+            const uint32_t i = base + r * kConsumers;
+            if (i >= total) break;  // the same for the whole warp
+            const uint32_t u = i >> 4, c = (i >> 2) & 3, piece = i & 3;  // unit, quarter, 16-k piece of the quarter
+            int q[16], qsum;
+            float scale;
+            quantize16<XDT>(raw[r], q, scale, qsum);
+            if (i >= items) continue;
+            // q + 128 = 256 * hi + (lo + 128): hi is its byte 1, lo its byte 0 with the top bit flipped
+            uint32_t rh[4], rl[4];
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t t[4];
+#pragma unroll
+                for (int b = 0; b < 4; b++) t[b] = (uint32_t)(q[TY == T_Q2_0 ? 4 * b + w : 4 * w + b] + 128);
+                rh[w] = __byte_perm(__byte_perm(t[0], t[1], 0x0051), __byte_perm(t[2], t[3], 0x0051), 0x5410);
+                rl[w] = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410) ^ 0x80808080u;
+            }
+            uint8_t *dst = xs + u * kXqUnit + xq_piece_offset(c, piece);
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(rh[0], rh[1], rh[2], rh[3]);
+            *reinterpret_cast<uint4 *>(dst + L.es) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
+            if ((piece & 1) == 0) {
+                float *f = reinterpret_cast<float *>(info + u * 4 + c);
+                f[piece >> 1] = scale;
+                f[2 + (piece >> 1)] = scale * (float)qsum;
+            }
         }
     }
 }
@@ -433,7 +461,8 @@ __device__ __forceinline__ void stage_x_halves(uint8_t *xs, const GemvLayout &L,
         const uint32_t u = it >> 4, c = (it >> 2) & 3, piece = it & 3;
         int q[16], qsum;
         float scale;
-        quantize16<XDT>(x, (size_t)col * kdim + (size_t)(u_first + u) * 256 + c * 64 + piece * 16, live, q, scale, qsum);
+        quantize16<XDT>(load16<XDT>(x, (size_t)col * kdim + (size_t)(u_first + u) * 256 + c * 64 + piece * 16, live), q, scale,
+                        qsum);
         if (!live) continue;
         float hi[16], lo[16];
 #pragma unroll
@@ -610,7 +639,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     uint32_t xs_ustride;
     if constexpr (SEP) {
         x_active = (g >> 1) == c;
-        xs_mine = xs + (g & 1) * L.es + c * kXqQuarter;
+        xs_mine = xs + (g & 1) * L.es + c * 64;
         xs_ustride = kXqUnit;
     } else {
         x_active = (g & 3) < p.n;
@@ -619,6 +648,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         if (tid < kZeroBytes / 4) reinterpret_cast<uint32_t *>(zeros)[tid] = 0u;
     }
 
+    const uint32_t xq_swap = (c >> 1) * 16;
     RingPos rp;
     uint32_t rot = 0;  // the deal of units to warps rotates from step to step
     for (uint32_t gb = 0; gb < ntl; gb += L.group) {
@@ -679,11 +709,12 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                             float acc[2] = {0.f, 0.f};
                             do {
                                 uint32_t xf[16];
-                                const uint4 *xp = reinterpret_cast<const uint4 *>(xs_mine + (pu + u) * xs_ustride);
+                                const uint8_t *xp = xs_mine + (pu + u) * xs_ustride;
 #pragma unroll
                                 for (int q = 0; q < 4; q++) {
                                     uint4 w4 = make_uint4(0u, 0u, 0u, 0u);
-                                    if (x_active) w4 = xp[q];
+                                    // quarters 2 and 3 keep their pieces swapped in pairs
+                                    if (x_active) w4 = lds128(xp + (q >> 1) * 32 + ((q & 1) ? 16 - xq_swap : xq_swap));
                                     xf[4 * q] = w4.x; xf[4 * q + 1] = w4.y; xf[4 * q + 2] = w4.z; xf[4 * q + 3] = w4.w;
                                 }
                                 const uint32_t off = (ubase + u) * UB;
@@ -783,6 +814,9 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
     // when the row size is a multiple of 64 bytes the rows a warp reads together
     // sit on the same banks, and per-row copies with a padded stride come first.
     const bool same_banks = row_bytes % 64 == 0;
+    GemvArgs fb_a = a;
+    GemvLayout fb_L = L;
+    bool have_fallback = false;
     for (uint32_t plan = 0; plan < 3 + nunit; plan++) {
         uint32_t nchunk, cb, rs, stage;
         L.tps = 1;
@@ -839,9 +873,16 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
         L.zero_off = (L.red_off + red_bytes + 15) & ~15u;
         L.tab_off = (L.zero_off + kZeroBytes + 15) & ~15u;
         L.smem_bytes = L.tab_off + tab_bytes;
-        if (L.smem_bytes <= budget) return true;
+        if (L.smem_bytes > budget) continue;
+        // A plan that keeps all of x resident stages it once per launch; one that does
+        // not stages a slice per k-chunk, every time with all warps waiting.  Prefer
+        // the first, as long as its row segments stay above 1 KB.
+        if (panel == nchunk) return true;
+        if (!have_fallback) { fb_a = a; fb_L = L; have_fallback = true; }
+        if ((nunit / (nchunk + 1)) * ub < 1024) break;
     }
-    return false;
+    if (have_fallback) { a = fb_a; L = fb_L; }
+    return have_fallback;
 }
 
 template <int TY, int XDT, bool SEP>
