@@ -783,23 +783,27 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     OKF_GEMV_TRACE(8);
 }
 
-// Shared-memory plan.  Two CTAs share an SM (this kernel's and the next one's,
-// already prefetching), so each gets at most 112 KB.
+// Shared-memory plan.  Two CTAs share an SM (this launch's and the next one's,
+// already prefetching), so each gets at most 112 KB.  (A launch with many tiles
+// per CTA gains nothing from taking the SM for itself with a deeper ring: at
+// that size the kernel is bound by instruction issue, not by bytes in flight.)
 //
 // Ring stages.  A bulk copy costs the copy engine about 50 ns however small it
-// is, and a stage hand-over costs the producer a few hundred, so stages are
-// large (20 - 46 KB) and filled by as few copies as possible: when whole rows fit,
-// a stage is up to four tiles (or half a tile) of consecutive rows and one
+// is, and a stage hand-over costs the consumers a few hundred cycles, so stages
+// are large (20 - 46 KB) and filled by as few copies as possible: when whole rows
+// fit, a stage is up to four tiles (or half a tile) of consecutive rows and one
 // contiguous copy -- which also makes the 2-byte-aligned layouts copyable, since
 // 8 rows always start on a 16-byte boundary -- otherwise rows are cut into
-// segments of at least 2.4 KB, one copy per row, which needs 16-byte aligned rows
-// and segments.  `tiles_per_cta` is the most tiles any CTA of the launch gets.
+// segments of at least 1 KB, one copy per row.  `tiles_per_cta` is the most tiles
+// any CTA of the launch gets.
+constexpr uint32_t kSharedBudget = 112 * 1024;
+
 static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, GemvArgs &a,
                         GemvLayout &L) {
     const uint32_t ub = ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
     L.nc = sep ? 1 : n;
     L.ecols = sep ? 2 : 8;
-    const uint32_t budget = 112 * 1024;
+    const uint32_t budget = kSharedBudget;
     const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
     L.group = 8192 / per_tile;
     if (L.group < 1) L.group = 1;
@@ -893,7 +897,7 @@ static cudaError_t launch_t(GemvArgs a, cudaStream_t s, int sms, int dev) {
     static bool attr_set[64] = {};  // the opt-in is per device
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<TY, XDT, SEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<TY, XDT, SEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedBudget);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }

@@ -1,23 +1,24 @@
 // Building blocks of the decode matvec (1..8 activation columns): mbarrier /
-// bulk-copy pipeline primitives, the warp MMA, activation fragments.
+// bulk-copy pipeline primitives, the fp16 warp MMA of the multi-column variant.
 //
 // Data path.  Weights stream from HBM into a shared-memory ring with bulk
 // asynchronous copies (cp.async.bulk, completion counted on an mbarrier) issued
 // by one producer thread, so a CTA has its whole share of a small matrix in
-// flight at once.  Consumer warps unpack the blocks from shared memory into
-// exact small integers held in fp16 and multiply them with the activations on
-// the tensor cores (mma.sync m16n8k16, fp32 accumulate); block scales are
-// applied to fp32 partial sums.
+// flight at once.  Consumer warps feed the blocks from shared memory to the
+// tensor cores (mma.sync m16n8k32 on bytes with s32 sums for one column, m16n8k16
+// on fp16 with fp32 sums for several); block scales are applied to the partial
+// sums in fp32.
 //
-// MMA operand layout (A = weights 16 rows x 16 k, B = activations 16 k x 8
-// columns): thread (g = lane / 4, c = lane % 4) holds A rows g and g + 8 and B
-// column g, both at k-slots {2c, 2c+1, 2c+8, 2c+9}.  A dot product does not care
-// which real k a slot stands for as long as A and B agree, so thread c simply
-// owns k in [64c, 64c + 64) of every 256-wide unit of a row.
+// MMA operand layout (A = weights, 16 rows; B = activations, 8 columns): thread
+// (g = lane / 4, c = lane % 4) holds A rows g and g + 8 and B column g, both at
+// the k-slots that belong to c.  A dot product does not care which real k a slot
+// stands for as long as A and B agree, so thread c simply owns k in
+// [64c, 64c + 64) of every 256-wide unit of a row.
 //
 // Every wait on an mbarrier is bounded: after about a second without progress
-// the thread records a code in the status word, raises the CTA's abort flag and
-// leaves; the other threads see the flag in their own waits and leave too.
+// the thread records a code in the status word and raises the CTA's abort flag;
+// the other waits see the flag and give up too, and the warps walk through the
+// rest of their loops without waiting, so every barrier among them still matches.
 #pragma once
 #include "okf_blocks.cuh"
 
@@ -55,7 +56,7 @@ __device__ __forceinline__ GemvSeg gemv_segment(const GemvArgs &p, uint32_t tile
     return s;
 }
 
-constexpr int kGemvWarps = 8;                      // consumer warps
+constexpr int kGemvWarps = 8;                      // consumer warps (a power of two; 16 measured no faster)
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;  // + one producer warp
 constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
 constexpr uint32_t kSpinLimit = 1u << 16;          // polls when draining on the way out
@@ -89,6 +90,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait.  Returns false if it gave up or the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
                                           int *status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;  // the usual case: the phase is over
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
@@ -146,18 +148,14 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// ---- activations in shared memory -----------------------------------------------
-// A slice of x (all effective columns, `nu` units of 256 k) is converted to fp16
-// once and kept in shared memory in the order the MMA wants it: the 64 values
-// that thread c of a quad owns in unit u of effective column e start at
+// ---- fp16 activation panel of the multi-column variant ----------------------------
+// A slice of x (the columns of one pass, `nu` units of 256 k) is kept in shared
+// memory as fp16 in the order the MMA wants it: the 64 values that thread c of a
+// quad owns in unit u of panel column e start at
 //     e * es + u * kXsUnit + c * 144          (es % 128 == 64)
-// so the eight lanes that read together (two columns or rows x four c) hit
-// eight different 16-byte bank groups.
-//
-// Effective columns: fp16 / bf16 activations have one per real column; fp32
-// activations have two, x = hi + lo with hi = fp16(x) (22 significant bits in
-// all): column e is hi of x[e], column lo_off + e is lo.  Magnitudes are
-// clamped to the fp16 range first.
+// so the eight lanes that read together (two columns x four c) hit eight
+// different 16-byte bank groups.  Panel column j holds the hi halves of real
+// column j, column 4 + j the lo halves: x = hi + lo with hi = fp16(x).
 constexpr uint32_t kXsUnit = 4 * 144;
 
 __host__ __device__ inline uint32_t xs_col_stride(uint32_t cb) {
@@ -165,58 +163,8 @@ __host__ __device__ inline uint32_t xs_col_stride(uint32_t cb) {
     return raw + ((64u + 128u - raw % 128u) % 128u);
 }
 
-template <int XDT>
-__device__ __forceinline__ float load_x_as_f32(const void *x, size_t idx) {
-    if constexpr (XDT == DT_F16) return __half2float(__ldg(reinterpret_cast<const __half *>(x) + idx));
-    else if constexpr (XDT == DT_BF16) return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16 *>(x) + idx));
-    else return __ldg(reinterpret_cast<const float *>(x) + idx);
-}
-
 __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-}
-
-// Cooperative load of the panel of units [u_first, u_first + nu) by `nthreads`
-// threads.  fp16 activations that are 16-byte aligned go global -> shared with
-// asynchronous 16-byte copies; everything else is converted in registers.
-// The caller waits with cp_async_wait_all() and a barrier.
-template <int XDT>
-__device__ __forceinline__ void stage_x_panel(uint8_t *xs, uint32_t es, const void *x, uint32_t kdim,
-                                              uint32_t n, uint32_t lo_off, uint32_t u_first, uint32_t nu,
-                                              uint32_t tid, uint32_t nthreads) {
-    const uint32_t k0 = u_first * 256;
-    if constexpr (XDT == DT_F16) {
-        if (((uintptr_t)x % 16) == 0) {
-            const uint32_t pieces_per_col = nu * 32;  // 16-byte pieces of eight k
-            for (uint32_t i = tid; i < n * pieces_per_col; i += nthreads) {
-                const uint32_t col = i / pieces_per_col, pc = i % pieces_per_col;
-                const uint32_t u = pc >> 5, c = (pc >> 3) & 3, q = pc & 7;
-                cp_async16(xs + col * es + u * kXsUnit + c * 144 + q * 16,
-                           reinterpret_cast<const __half *>(x) + (size_t)col * kdim + k0 + pc * 8);
-            }
-            return;
-        }
-    }
-    const uint32_t pairs_per_col = nu * 128;  // two k per item
-    for (uint32_t i = tid; i < n * pairs_per_col; i += nthreads) {
-        const uint32_t col = i / pairs_per_col, kk = (i % pairs_per_col) * 2;
-        const uint32_t u = kk >> 8, c = (kk >> 6) & 3, r = kk & 63;
-        const uint32_t off = u * kXsUnit + c * 144 + r * 2;
-        const size_t src = (size_t)col * kdim + k0 + kk;
-        float a = load_x_as_f32<XDT>(x, src), b = load_x_as_f32<XDT>(x, src + 1);
-        a = fminf(fmaxf(a, -65504.f), 65504.f);
-        b = fminf(fmaxf(b, -65504.f), 65504.f);
-        const uint32_t hi = pack_h2(a, b);
-        *reinterpret_cast<uint32_t *>(xs + col * es + off) = hi;
-        if constexpr (XDT == DT_F32) {
-            const __half2 h = *reinterpret_cast<const __half2 *>(&hi);
-            *reinterpret_cast<uint32_t *>(xs + (lo_off + col) * es + off) =
-                pack_h2(a - __low2float(h), b - __high2float(h));
-        }
-    }
 }
 
 // byte b (0..255) of `v` as a float, without the slow int-to-float unit
