@@ -23,6 +23,9 @@
 //
 // Every mbarrier wait is bounded (about a second); a wait that gives up records
 // a code in the status word, the CTA frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <cstring>
 #include "okf_gemv_mma.cuh"
 #include "okf_internal.h"
 #include "okf_kernels.h"
@@ -38,10 +41,12 @@ constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KB
 constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KB per 256 tokens
 constexpr uint32_t kRingBytes = 4 * (kABytes + kBBytes);  // four stages of one token block, or two of two
 constexpr uint32_t kAWarps = 8;                        // warps 0..7 unpack weights (A tile)
-constexpr uint32_t kBWarps = 8;                        // warps 8..15 copy activations (B tile)
+constexpr uint32_t kBWarps = 8;                        // warps 8..15: fp32 activations: convert the B tile;
+                                                       // 16-bit activations: a second unpacking group
 constexpr uint32_t kProducerWarps = kAWarps + kBWarps;
-constexpr uint32_t kMmaWarp = kProducerWarps;          // warp 16
-constexpr uint32_t kThreads = (kProducerWarps + 1 + 4) * 32;  // + MMA warp + four epilogue warps
+constexpr uint32_t kTmaWarp = kProducerWarps;          // warp 16: one thread hands B tiles to the copy engine
+constexpr uint32_t kMmaWarp = kProducerWarps + 1;      // warp 17
+constexpr uint32_t kThreads = (kProducerWarps + 2 + 4) * 32;  // + four epilogue warps
 constexpr uint32_t kSmemBytes = 1024 /*align*/ + kRingBytes + 2048 /*grid*/ + 256 /*barriers*/;
 constexpr int kStatusGemmTimeout = 3;
 
@@ -54,7 +59,51 @@ struct Args {
     uint32_t row_bytes;
     uint32_t ksplit;   // work items per (slab, token group): each takes a range of k-blocks
     float *partial;    // ksplit > 1: fp32 partial results [ksplit][n][m], summed by a second kernel
+    // ksplit == 1: the last tail_items (slab, token block) items -- what is left after
+    // the full waves -- are cut into tail_parts runs of tail_tok tokens, one per CTA
+    uint32_t tail_items, tail_tok, tail_parts;
 };
+
+// One piece of work of a CTA: rows [mt * 128, +128) x tokens [n0, n0 + ntok) x k-blocks [kb0, kb1).
+struct Work {
+    uint32_t mt, n0, ntok, kb0, kb1, part;
+};
+
+// The j-th piece of work of this CTA; false when there is none.  Whole items go
+// round-robin over the CTAs; with a tail split every CTA then takes one run of
+// tokens of one of the left-over items (NACC == 1 only).
+template <int NACC>
+__device__ __forceinline__ bool next_work(const Args &p, uint32_t j, Work &w) {
+    const uint32_t m_tiles = (p.m + kBM - 1) / kBM;
+    const uint32_t n_groups = (p.n + NACC * kBN - 1) / (NACC * kBN);
+    const uint32_t kblocks = p.k / kBK;
+    const uint32_t base = m_tiles * n_groups;
+    const uint32_t item = blockIdx.x + j * gridDim.x;
+    if (p.ksplit > 1) {  // k-range fastest, then token group, then slab
+        if (item >= base * p.ksplit) return false;
+        w.mt = item / (n_groups * p.ksplit);
+        w.n0 = ((item / p.ksplit) % n_groups) * (NACC * kBN);
+        w.ntok = NACC * kBN;
+        w.part = item % p.ksplit;
+        w.kb0 = (uint32_t)((uint64_t)kblocks * w.part / p.ksplit);
+        w.kb1 = (uint32_t)((uint64_t)kblocks * (w.part + 1) / p.ksplit);
+        return true;
+    }
+    w.part = 0; w.kb0 = 0; w.kb1 = kblocks;
+    const uint32_t whole = p.tail_tok ? base - p.tail_items : base;  // a multiple of the grid when there is a tail
+    if (item < whole) {
+        w.mt = item / n_groups;
+        w.n0 = (item % n_groups) * (NACC * kBN);
+        w.ntok = NACC * kBN;
+        return true;
+    }
+    if (!p.tail_tok || j != whole / gridDim.x || blockIdx.x >= p.tail_items * p.tail_parts) return false;
+    const uint32_t t_item = whole + blockIdx.x / p.tail_parts;
+    w.mt = t_item / n_groups;
+    w.n0 = (t_item % n_groups) * (NACC * kBN) + (blockIdx.x % p.tail_parts) * p.tail_tok;
+    w.ntok = p.tail_tok;
+    return true;
+}
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -178,6 +227,18 @@ __device__ __forceinline__ void cp_async16_arrive(uint64_t *bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One 2-D tile of the activations, global -> shared, through the tensor map: box =
+// 64 k x 256 tokens, written in the 128-byte-swizzled layout the MMA reads; tokens
+// past the end of X come back as zeros.  x is the element index along k (a multiple
+// of 8, so the copy starts on a 16-byte boundary), y the token.
+__device__ __forceinline__ void tma_load_tile(void *dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // One lane polls, the warp follows.  Producers that run ahead sleep between polls
 // so they do not take issue slots from the warps doing the unpacking.
 __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32_t lane, volatile int *abort_flag,
@@ -199,9 +260,9 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32
 
 // NACC: token blocks (accumulators) per work item, 1 or 2.
 template <int TY, int XDT, typename OT, int NACC>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __grid_constant__ CUtensorMap xmap) {
     constexpr bool F16 = XDT == DT_F16;
-    constexpr bool ASYNC_B = XDT != DT_F32;  // 16-bit activations are copied, fp32 ones converted
+    constexpr bool ASYNC_B = XDT != DT_F32;  // 16-bit activations come by TMA, fp32 ones are converted by eight warps
     constexpr uint32_t kStageBytes = kABytes + NACC * kBBytes;
     constexpr uint32_t kStages = kRingBytes / kStageBytes;  // 4 or 2
     extern __shared__ uint8_t smem_raw[];
@@ -217,19 +278,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t m_tiles = (p.m + kBM - 1) / kBM;
-    const uint32_t n_groups = (p.n + NACC * kBN - 1) / (NACC * kBN);  // token groups of NACC blocks
-    const uint32_t kblocks_all = p.k / kBK;
-    const uint32_t items = m_tiles * n_groups * p.ksplit;  // k-range fastest, then token group, then slab
-    // item -> slab, token group and the range of k-blocks [kb0, kb0 + kblocks)
-    auto item_mt = [&](uint32_t item) { return item / (n_groups * p.ksplit); };
-    auto item_ng = [&](uint32_t item) { return (item / p.ksplit) % n_groups; };
-    auto item_kb0 = [&](uint32_t item) { return (uint32_t)((uint64_t)kblocks_all * (item % p.ksplit) / p.ksplit); };
-    auto item_kb1 = [&](uint32_t item) { return (uint32_t)((uint64_t)kblocks_all * (item % p.ksplit + 1) / p.ksplit); };
-
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) {
-            mbar_init(&full[s], kAWarps + (ASYNC_B ? kBWarps * 32 : kBWarps));
+            mbar_init(&full[s], kAWarps + (ASYNC_B ? 1 : kBWarps));
             mbar_init(&empty[s], 1);
         }
         for (uint32_t a = 0; a < 2; a++) {
@@ -252,22 +303,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < kAWarps) {
-        // ---------------- A producers: unpack 128 rows x 64 weights into swizzled shared memory
-        const uint32_t t = threadIdx.x;
+    if (warp < kAWarps || (ASYNC_B && warp < kProducerWarps)) {
+        // ---------------- A producers: unpack 128 rows x 64 weights into swizzled shared memory.
+        // With 16-bit activations there are two groups of eight warps that take the k-blocks
+        // in turn: one k-block's latency (load, decode, wait, store, fence) is longer than the
+        // MMAs it feeds, two in flight are not.
+        constexpr uint32_t kGroups = ASYNC_B ? 2 : 1;
+        const uint32_t grp = warp / kAWarps;
+        const uint32_t t = threadIdx.x % (kAWarps * 32);
         const uint32_t arow = t >> 1, ahalf = t & 1;  // thread t unpacks 32 weights of row arow
-        uint32_t it = 0;  // running stage counter
-        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-            const uint32_t m0 = item_mt(item) * kBM;
-            const uint32_t kb0 = item_kb0(item), kb1 = item_kb1(item);
+        uint32_t it0 = 0;  // stage counter at the start of the work item
+        Work wk;
+        for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
+            const uint32_t m0 = wk.mt * kBM;
+            const uint32_t kb0 = wk.kb0, kb1 = wk.kb1;
             const uint32_t wrow = min(m0 + arow, p.m - 1);
             const uint8_t *wp = p.w + (size_t)wrow * p.row_bytes;
             const bool arow_live = m0 + arow < p.m;
+            // this group's first k-block: the one whose stage counter has its parity
+            const uint32_t first = kb0 + (kGroups == 2 ? ((grp + it0) & 1) : 0);
             ARaw<TY> cur, nxt;
-            cur.load(wp, kb0, ahalf);
-            for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
+            if (first < kb1) cur.load(wp, first, ahalf);
+            for (uint32_t kb = first; kb < kb1; kb += kGroups) {
+                const uint32_t it = it0 + (kb - kb0);
                 const uint32_t s = it % kStages, use = it / kStages;
-                if (kb + 1 < kb1) nxt.load(wp, kb + 1, ahalf);
+                if (kb + kGroups < kb1) nxt.load(wp, kb + kGroups, ahalf);
                 float v[32];
                 cur.decode(v, grid);
                 uint4 q[4];
@@ -287,32 +347,55 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
                 if (lane == 0) mbar_arrive(&full[s]);
                 cur = nxt;
             }
+            it0 += kb1 - kb0;
+        }
+    } else if (warp == kTmaWarp) {
+        // ---------------- B tiles of 16-bit activations: NACC x 256 tokens x 64 k per stage
+        if constexpr (ASYNC_B) {
+            if (lane == 0) {
+                uint32_t it = 0;
+                Work wk;
+                for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
+                    const uint32_t nblk = wk.ntok > kBN ? NACC : 1;
+                    for (uint32_t kb = wk.kb0; kb < wk.kb1; kb++, it++) {
+                        const uint32_t s = it % kStages, use = it / kStages;
+                        if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
+                            // giving up: the copies already handed over land within microseconds;
+                            // stay for a while so that they do not write into a CTA that has gone
+                            const long long t0 = clock64();
+                            while (clock64() - t0 < 100000) {}
+                            goto done;
+                        }
+                        uint8_t *sb = stage0 + (size_t)s * kStageBytes + kABytes;
+                        mbar_expect_tx(&full[s], nblk * kBBytes);
+                        for (uint32_t a = 0; a < nblk; a++)
+                            tma_load_tile(sb + a * kBBytes, &xmap, kb * kBK, wk.n0 + a * kBN, &full[s]);
+                    }
+                }
+            }
         }
     } else if (warp < kProducerWarps) {
-        // ---------------- B producers: NACC x 256 tokens x 64 activations per stage
-        const uint32_t t = threadIdx.x - kAWarps * 32;  // 0..255
-        constexpr uint32_t kChunks = NACC * kBN * 8 / (kBWarps * 32);  // 16-byte chunks per thread: 8 or 16
-        uint32_t it = 0;
-        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-            const uint32_t n0 = item_ng(item) * (NACC * kBN);
-            const uint32_t kb0 = item_kb0(item), kb1 = item_kb1(item);
-            for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
-                const uint32_t s = it % kStages, use = it / kStages;
-                if (use > 0 && !warp_wait(&empty[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
-                uint8_t *sb = stage0 + (size_t)s * kStageBytes + kABytes;
+        // ---------------- B tiles of fp32 activations: eight warps convert them
+        if constexpr (!ASYNC_B) {
+            const uint32_t t = threadIdx.x - kAWarps * 32;  // 0..255
+            constexpr uint32_t kChunks = NACC * kBN * 8 / (kBWarps * 32);  // 16-byte chunks per thread
+            uint32_t it = 0;
+            Work wk;
+            for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
+                const uint32_t n0 = wk.n0;
+                for (uint32_t kb = wk.kb0; kb < wk.kb1; kb++, it++) {
+                    const uint32_t s = it % kStages, use = it / kStages;
+                    if (use > 0 && !warp_wait(&empty[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
+                    uint8_t *sb = stage0 + (size_t)s * kStageBytes + kABytes;
 #pragma unroll
-                for (uint32_t i = 0; i < kChunks; i++) {
-                    const uint32_t q = t + kBWarps * 32 * i;
-                    const uint32_t row = q >> 3, j = q & 7;  // row over NACC x 256 tokens; blocks are 32 KB apart
-                    const uint32_t tok = n0 + row;
-                    uint8_t *dst = sb + (row >> 8) * kBBytes + swz(row & 255, j);
-                    const size_t e = (size_t)min(tok, p.n - 1) * p.k + (size_t)kb * kBK + j * 8;
-                    if constexpr (ASYNC_B) {
-                        if (tok < p.n) cp_async16(dst, reinterpret_cast<const uint16_t *>(p.x) + e);
-                        else *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
-                    } else {
+                    for (uint32_t i = 0; i < kChunks; i++) {
+                        const uint32_t q = t + kBWarps * 32 * i;
+                        const uint32_t row = q >> 3, c16 = q & 7;  // row over NACC x 256 tokens; blocks are 32 KB apart
+                        const uint32_t tok = n0 + row;
+                        uint8_t *dst = sb + (row >> 8) * kBBytes + swz(row & 255, c16);
+                        const size_t e = (size_t)min(tok, p.n - 1) * p.k + (size_t)kb * kBK + c16 * 8;
                         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                        if (tok < p.n) {
+                        if (tok < p.n && row < wk.ntok) {
                             const float4 f0 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + e));
                             const float4 f1 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + e) + 1);
                             v.x = pack16<false>(f0.x, f0.y); v.y = pack16<false>(f0.z, f0.w);
@@ -320,10 +403,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
                         }
                         *reinterpret_cast<uint4 *>(dst) = v;
                     }
-                }
-                if constexpr (ASYNC_B) {
-                    cp_async16_arrive(&full[s]);  // every thread: fires when its copies have landed
-                } else {
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full[s]);
@@ -336,8 +415,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
         // k-block by k-block, 32 bytes per row at a time.
         if (lane == 1) {
             uint32_t last_mt = 0xFFFFFFFFu;
-            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-                const uint32_t mt = item_mt(item);
+            Work wk;
+            for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
+                const uint32_t mt = wk.mt;
                 if (mt == last_mt) continue;  // same slab as the previous item
                 last_mt = mt;
                 const uint32_t m0 = mt * kBM;
@@ -352,9 +432,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
             }
         }
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(F16 ? 0u : 1u, kBM, kBN);
             uint32_t it = 0, tile = 0;
-            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, tile++) {
+            Work wk;
+            for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++, tile++) {
+                // N of the instruction: a whole block, or the tokens of a short run
+                const uint32_t idesc = instr_desc(F16 ? 0u : 1u, kBM, wk.ntok < kBN ? wk.ntok : kBN);
                 // accumulators: both for a two-block item, alternating for one-block items
                 const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
                 bool ok = true;
@@ -362,11 +444,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
                     if (acc_use > 0) ok = mbar_wait(&acc_empty[acc0 + a], (acc_use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t kb0 = item_kb0(item), kb1 = item_kb1(item);
+                const uint32_t kb0 = wk.kb0, kb1 = wk.kb1;
                 for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
                     const uint32_t s = it % kStages, use = it / kStages;
                     if (!mbar_wait(&full[s], use & 1, abort_flag, p.status, kStatusGemmTimeout)) { ok = false; break; }
-                    fence_proxy_async();  // the asynchronous copies wrote through the generic proxy
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage0 + (size_t)s * kStageBytes);
                     const uint64_t da = smem_desc(sa);
@@ -390,19 +471,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
         // ---------------- epilogue: four warps, warp q reads tensor-memory lanes 32q .. 32q + 31
         const uint32_t q = warp & 3;  // a warp may only touch the lane quarter given by warp id % 4
         uint32_t tile = 0;
-        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, tile++) {
-            const uint32_t mt = item_mt(item), n0 = item_ng(item) * (NACC * kBN);
+        Work wk;
+        for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++, tile++) {
+            const uint32_t mt = wk.mt, n0 = wk.n0;
+            const uint32_t n_end = min(p.n, n0 + wk.ntok);
             const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
             const uint32_t row = mt * kBM + q * 32 + lane;
             OT *out = reinterpret_cast<OT *>(p.out);
-            float *part = p.ksplit > 1 ? p.partial + (size_t)(item % p.ksplit) * p.n * p.m : nullptr;
+            float *part = p.ksplit > 1 ? p.partial + (size_t)wk.part * p.n * p.m : nullptr;
             for (uint32_t a = 0; a < (uint32_t)NACC; a++) {
                 const uint32_t acc = acc0 + a;
                 if (!warp_wait(&acc_full[acc], acc_use & 1, lane, abort_flag, p.status)) goto done;
                 tc_fence_after();
 #pragma unroll 1
                 for (uint32_t c0 = 0; c0 < kBN; c0 += 32) {
-                    if (n0 + a * kBN + c0 >= p.n) break;  // nothing but padding from here on
+                    if (n0 + a * kBN + c0 >= n_end) break;  // nothing but padding from here on
                     uint32_t r[32];
                     tmem_ld32(tmem_base + ((q * 32) << 16) + acc * kBN + c0, r);
                     tmem_ld_wait();
@@ -410,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
                             const uint32_t tok = n0 + a * kBN + c0 + j;
-                            if (tok < p.n) {
+                            if (tok < n_end) {
                                 const float f = __uint_as_float(r[j]);
                                 if (part) part[(size_t)tok * p.m + row] = f;
                                 else if constexpr (sizeof(OT) == 4) out[(size_t)tok * p.m + row] = f;
@@ -462,6 +545,31 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
     }
 }
 
+// Tensor map of the activations X[n][k] (16-bit elements) for tma_load_tile.  The
+// driver's encoder is looked up once; nothing is linked against libcuda.
+static cudaError_t encode_x_map(CUtensorMap *map, const void *x, uint32_t k, uint32_t n) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (q != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+        encode = (EncodeFn)fn;
+    }
+    const cuuint64_t dims[2] = {k, n};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {kBK, kBN};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(x), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 template <int TY, int XDT, typename OT, int NACC>
 static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
     static bool attr_set[64] = {};  // the opt-in is per device
@@ -472,8 +580,14 @@ static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
         attr_set[dev] = true;
     }
     const uint32_t items = ((a.m + kBM - 1) / kBM) * ((a.n + NACC * kBN - 1) / (NACC * kBN)) * a.ksplit;
-    const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;
-    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, kSmemBytes, s>>>(a);
+    const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;  // a tail split always has items > sms
+    alignas(64) CUtensorMap xmap;
+    memset(&xmap, 0, sizeof(xmap));
+    if constexpr (XDT != DT_F32) {
+        cudaError_t me = encode_x_map(&xmap, a.x, a.k, a.n);
+        if (me != cudaSuccess) return me;
+    }
+    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, kSmemBytes, s>>>(a, xmap);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || a.ksplit == 1) return e;
     const size_t count = (size_t)a.n * a.m;
@@ -481,51 +595,79 @@ static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
     return cudaGetLastError();
 }
 
-// Two token blocks per item halve the unpacking per flop, but only pay when the
-// slabs alone can fill the GPU; fp32 activations (converted in registers) stay
-// with one block.
 template <int TY, int XDT, typename OT>
-static cudaError_t launch(const Args &a, cudaStream_t s, int sms, int dev) {
-    if (XDT != DT_F32 && a.n > kBN) return launch_n<TY, XDT, OT, 2>(a, s, sms, dev);
+static cudaError_t launch(const Args &a, uint32_t nacc, cudaStream_t s, int sms, int dev) {
+    if constexpr (XDT != DT_F32) {
+        if (nacc == 2) return launch_n<TY, XDT, OT, 2>(a, s, sms, dev);
+    }
     return launch_n<TY, XDT, OT, 1>(a, s, sms, dev);
 }
 
 template <int TY, int XDT>
-static cudaError_t launch_o(const Args &a, int odt, cudaStream_t s, int sms, int dev) {
-    if (odt == DT_F32) return launch<TY, XDT, float>(a, s, sms, dev);
-    if (odt == DT_BF16) return launch<TY, XDT, __nv_bfloat16>(a, s, sms, dev);
+static cudaError_t launch_o(const Args &a, uint32_t nacc, int odt, cudaStream_t s, int sms, int dev) {
+    if (odt == DT_F32) return launch<TY, XDT, float>(a, nacc, s, sms, dev);
+    if (odt == DT_BF16) return launch<TY, XDT, __nv_bfloat16>(a, nacc, s, sms, dev);
     return cudaErrorInvalidValue;
 }
 
 template <int TY>
-static cudaError_t launch_x(const Args &a, int xdt, int odt, cudaStream_t s, int sms, int dev) {
+static cudaError_t launch_x(const Args &a, uint32_t nacc, int xdt, int odt, cudaStream_t s, int sms, int dev) {
     switch (xdt) {
-    case DT_F16: return launch_o<TY, DT_F16>(a, odt, s, sms, dev);
-    case DT_BF16: return launch_o<TY, DT_BF16>(a, odt, s, sms, dev);
-    case DT_F32: return launch_o<TY, DT_F32>(a, odt, s, sms, dev);
+    case DT_F16: return launch_o<TY, DT_F16>(a, nacc, odt, s, sms, dev);
+    case DT_BF16: return launch_o<TY, DT_BF16>(a, nacc, odt, s, sms, dev);
+    case DT_F32: return launch_o<TY, DT_F32>(a, nacc, odt, s, sms, dev);
     default: return cudaErrorInvalidValue;
     }
 }
 
 }  // namespace tc
 
-// How many k-ranges to cut each (slab, token group) into so the work items fill
-// the GPU: the smallest split (up to 8, at least 16 k-blocks each) whose last
-// wave is at least 80 % full, else the fullest one.  A split needs
-// ksplit * n * m floats of scratch for the partial results.
-uint32_t gemm_tc_ksplit(uint32_t k, uint32_t m, uint32_t n, int xdt, int sms) {
-    const uint32_t nacc = (xdt != DT_F32 && n > tc::kBN) ? 2 : 1;
-    const uint32_t base = ((m + tc::kBM - 1) / tc::kBM) * ((n + nacc * tc::kBN - 1) / (nacc * tc::kBN));
-    const uint32_t kblocks = k / tc::kBK;
-    uint32_t best = 1;
-    double best_eff = 0.0;
-    for (uint32_t ks = 1; ks <= 8 && kblocks / ks >= 16; ks++) {
-        const uint32_t items = base * ks, waves = (items + sms - 1) / sms;
-        const double eff = (double)items / ((double)waves * sms);
-        if (eff >= 0.8) return ks;
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
+// How to lay a matmul over the SMs.  A work item is a 128-row slab against one
+// or two 256-token blocks over all of K or, with a split, over one of ksplit
+// k-ranges whose fp32 partial results a second kernel sums (ksplit * n * m floats
+// of scratch).  Without a split and with more items than SMs, the items left
+// after the full waves can be cut into short runs of tokens, one per CTA,
+// instead of costing a whole extra wave.  The plan with the smallest estimated
+// time wins.  The estimate: a CTA spends 1.04 us per k-block on an item of two
+// token blocks and 0.73 us on one of one block (the unpacking of the slab, not
+// the MMAs, sets the pace of a single block), a run of tokens costs no less than
+// 0.55 us per k-block, and the partial sums are written and read back at 5 TB/s
+// (figures measured on B200 with Q4_K weights).
+struct GemmPlan {
+    uint32_t nacc, ksplit, tail_items, tail_tok, tail_parts;
+};
+
+static GemmPlan gemm_tc_plan(uint32_t k, uint32_t m, uint32_t n, int xdt, int sms, uint32_t force_ksplit) {
+    const uint32_t slabs = (m + tc::kBM - 1) / tc::kBM, kblocks = k / tc::kBK;
+    GemmPlan best = {1, force_ksplit > 1 ? force_ksplit : 1, 0, 0, 0};
+    double best_t = 1e30;
+    for (uint32_t nacc = 1; nacc <= 2; nacc++) {
+        if (nacc == 2 && (xdt == DT_F32 || n <= tc::kBN)) continue;
+        const double t_kb = nacc == 2 ? 1.04e-6 : 0.73e-6;
+        const uint32_t base = slabs * ((n + nacc * tc::kBN - 1) / (nacc * tc::kBN));
+        for (uint32_t ks = 1; ks <= 8; ks++) {
+            if (force_ksplit ? ks != force_ksplit : (ks > 1 && kblocks / ks < 8)) continue;
+            if (ks > kblocks) continue;
+            const uint32_t items = base * ks, waves = (items + sms - 1) / sms;
+            const double per_item = (double)((kblocks + ks - 1) / ks) * t_kb;
+            const double t_red = ks > 1 ? (2.0 * ks + 1) * n * (double)m * 4 / 5e12 : 0.0;
+            const double t = waves * per_item + t_red;
+            if (t < best_t) { best_t = t; best = {nacc, ks, 0, 0, 0}; }
+            if (ks == 1 && nacc == 1 && base > (uint32_t)sms && base % sms) {
+                const uint32_t full_waves = base / sms, left = base % sms;
+                uint32_t tok = 16;
+                while (left * (tc::kBN / tok) > (uint32_t)sms) tok *= 2;
+                const double run = t_kb * tok / tc::kBN;
+                const double t2 = full_waves * per_item + kblocks * (run > 0.55e-6 ? run : 0.55e-6);
+                if (t2 < best_t) { best_t = t2; best = {1, 1, left, tok, tc::kBN / tok}; }
+            }
+        }
     }
     return best;
+}
+
+uint32_t gemm_tc_ksplit(uint32_t k, uint32_t m, uint32_t n, int xdt, int sms) {
+    return gemm_tc_plan(k, m, n, xdt, sms, 0).ksplit;
 }
 
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n) {
@@ -541,14 +683,17 @@ cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, con
                            cudaStream_t s, int sms, int dev) {
     tc::Args a;
     a.w = w; a.x = x; a.out = out; a.status = status; a.k = k; a.m = m; a.n = n;
-    a.ksplit = ksplit > 1 && partial ? ksplit : 1;
+    // the caller decides whether there is a split (it owns the scratch); the rest is planned here
+    const GemmPlan plan = gemm_tc_plan(k, m, n, xdt, sms, ksplit > 1 && partial ? ksplit : 1);
+    a.ksplit = plan.ksplit;
     a.partial = partial;
+    a.tail_items = plan.tail_items; a.tail_tok = plan.tail_tok; a.tail_parts = plan.tail_parts;
     a.row_bytes = (k / block_elems(ty)) * block_bytes(ty);
     switch (ty) {
-    case T_Q4_K: return tc::launch_x<T_Q4_K>(a, xdt, odt, s, sms, dev);
-    case T_Q8_0: return tc::launch_x<T_Q8_0>(a, xdt, odt, s, sms, dev);
-    case T_Q2_0: return tc::launch_x<T_Q2_0>(a, xdt, odt, s, sms, dev);
-    case T_IQ2_XXS: return tc::launch_x<T_IQ2_XXS>(a, xdt, odt, s, sms, dev);
+    case T_Q4_K: return tc::launch_x<T_Q4_K>(a, plan.nacc, xdt, odt, s, sms, dev);
+    case T_Q8_0: return tc::launch_x<T_Q8_0>(a, plan.nacc, xdt, odt, s, sms, dev);
+    case T_Q2_0: return tc::launch_x<T_Q2_0>(a, plan.nacc, xdt, odt, s, sms, dev);
+    case T_IQ2_XXS: return tc::launch_x<T_IQ2_XXS>(a, plan.nacc, xdt, odt, s, sms, dev);
     default: return cudaErrorInvalidValue;
     }
 }

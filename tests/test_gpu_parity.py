@@ -208,6 +208,23 @@ def test_gemm_vs_oracle(ctx, ty, xdt, odt):
         assert rel_err(o[:n * m].reshape(n, m), ref) <= tol, (ty, k, m, n)
 
 
+@pytest.mark.parametrize("m,n", [(6400, 768), (10240, 512), (9728, 500)])
+def test_gemm_more_items_than_sms(ctx, m, n):
+    """More (128-row slab, 256-token block) items than SMs with a few left over:
+    the left-over items are cut into short runs of tokens spread over the CTAs."""
+    ty, k = GGUFType.Q4_K, 256
+    blocks = make_weights(ty, m, k, seed=m)
+    X = np.random.default_rng(n).normal(size=(n, k)).astype(np.float32)
+    Xd = dev(X, torch.bfloat16)
+    ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
+    out = torch.full((n * m + 8,), float("nan"), dtype=torch.float32, device="cuda")
+    CudaEnc(ctx).gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
+    torch.cuda.synchronize()
+    o = out.cpu().numpy()
+    assert np.isnan(o[n * m:]).all()
+    assert rel_err(o[:n * m].reshape(n, m), ref) <= GEMM_TOL
+
+
 def test_gemm_split_k_odd_sizes(ctx):
     """A short, deep matrix makes the matmul cut K into ranges (partials in
     scratch, summed by a second kernel); M * N is odd on purpose."""
