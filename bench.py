@@ -192,8 +192,7 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": "quant GEMV HBM GB/s at b=1 (%s)" % args.workload, "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16" if tensor_bound else "int8", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "batch": 1, "activations": "widened to f32", "layers_per_step": 1},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -563,7 +562,10 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu captures summarised under profiles/ (None until captured)
-TRAFFIC = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (the decode figure is the mean of the two launches of a
+# layer: gate || up 28.06 MB, down 14.07 MB; the prefill one of its two shapes)
+TRAFFIC = {"q4k_ffn_gemv": 21.07e6, "q4k_prefill": 65.4e6}
 
 
 def main():
