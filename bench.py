@@ -207,7 +207,7 @@ class Layers:
     """Device-resident weights of a workload: per layer and matrix a distinct
     copy assembled from the block pool, plus activations and output buffers."""
 
-    def __init__(self, ctx, name, n, rank, world, layers=None):
+    def __init__(self, ctx, name, n, rank, world, layers=None, gather="fused"):
         import torch
 
         from chatokf_b200.enc import GGUFTensor
@@ -242,9 +242,17 @@ class Layers:
         self.bytes_per_step = algorithmic_bytes(mats, xdt, n) * self.layers
         self.weight_bytes_per_step = sum(row_byte_count(ty, k) * m for _, ty, k, m in mats) * self.layers
         self.flops_per_step = sum(2 * n * k * m for _, _, k, m in mats) * self.layers
+        # how the row shards' outputs reach every rank: "fused" = the matvec kernel stores into
+        # every rank's buffer itself (N <= 8), "nccl" = an all-gather after every launch,
+        # "none" = not at all (compute only, for comparison)
+        self.gather = gather if (world > 1 and (gather != "fused" or n <= 8)) else ("nccl" if world > 1 else "none")
         if world > 1:
             self.gathered = {m: torch.empty(world, n, m, dtype=torch.float32, device="cuda")
                              for m in {mm[3] for mm in self.mats}}
+        if self.gather == "fused":
+            from chatokf_b200 import tp
+
+            self.peers = tp.PeerOutputs(ctx, [(n, t.M * world) for t, _, _, _ in self.items])
 
     # Projections the reference's engines wrap in one MetalEnc.parallel region
     # (QwenMetalEngine.swift:464-469 gate || up, :691-696 q || k || v): they read the
@@ -262,14 +270,20 @@ class Layers:
             while region and j < len(self.items) and j // per_layer == i // per_layer \
                     and self.mats[j % per_layer][0] in region:
                 j += 1
+            def call(idx):
+                t, w, x, out = self.items[idx]
+                if self.gather == "fused":
+                    enc.gemm_gather(t, x, self.peers.slot(idx, t.M), w, self.n)
+                else:
+                    enc.gemm(t, x, out, w, self.n)
+
             if j - i > 1:
                 with enc.parallel():
-                    for t, w, x, out in self.items[i:j]:
-                        enc.gemm(t, x, out, w, self.n)
+                    for idx in range(i, j):
+                        call(idx)
             else:
-                t, w, x, out = self.items[i]
-                enc.gemm(t, x, out, w, self.n)
-            if self.world > 1:
+                call(i)
+            if self.gather == "nccl":
                 for t, w, x, out in self.items[i:j]:
                     dist.all_gather_into_tensor(self.gathered[t.M].view(-1), out.view(-1))
             i = j
@@ -457,7 +471,7 @@ def run_ours(args):
     enc = CudaEnc(ctx)
     stream = torch.cuda.Stream()
     wl, batch = args.workload, args.batch
-    L = Layers(ctx, wl, batch, rank, world)
+    L = Layers(ctx, wl, batch, rank, world, gather=args.gather)
     tensor_bound = batch > 8
 
     with torch.cuda.stream(stream):
@@ -525,7 +539,10 @@ def run_ours(args):
                    "launches_per_step": L.launches_per_step,
                    "parallel_regions": "gate || up and q || k || v leave as one launch each, as the "
                                        "reference's engines co-schedule them",
-                   "parallelism": f"rows/{world} + all-gather" if world > 1 else "single GPU",
+                   "parallelism": (f"rows/{world}, outputs to every rank by " +
+                                   {"fused": "stores from the matvec kernel into peer memory (no collective)",
+                                    "nccl": "an NCCL all-gather after every launch",
+                                    "none": "nothing (compute only)"}[L.gather]) if world > 1 else "single GPU",
                    "cuda_graph": graphed},
         "roofline": roof,
         "e2e": {"value": e2e_val, "unit": "TFLOP/s" if tensor_bound else "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -578,6 +595,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="which configuration is the timed one")
     ap.add_argument("--batch", type=int, default=1, help="activation columns (tokens) per call")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
+                    help="N > 1 GPUs: how every rank gets the whole output (fused needs batch <= 8)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

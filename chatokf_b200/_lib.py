@@ -49,6 +49,28 @@ SIGNATURES = {
     "okf_launch_count": (_u64, [_vp]),
 }
 
+
+
+class IpcHandle(ctypes.Structure):
+    """okf_ipc_handle"""
+    _fields_ = [("bytes", ctypes.c_ubyte * 64)]
+
+
+class Gather(ctypes.Structure):
+    """okf_gather"""
+    _fields_ = [("nranks", _u32), ("rank", _u32), ("m_total", _u32), ("row_first", _u32),
+                ("out", _vp * 8), ("arrivals", _vp * 8), ("epoch", _vp)]
+
+
+SIGNATURES.update({
+    "okf_shared_alloc": (_ci, [_vp, _sz, _pp, ctypes.POINTER(IpcHandle)]),
+    "okf_shared_open": (_ci, [_vp, ctypes.POINTER(IpcHandle), _pp]),
+    "okf_shared_close": (_ci, [_vp, _vp]),
+    "okf_shared_free": (_ci, [_vp, _vp]),
+    "okf_copy_to_host": (_ci, [_vp, _vp, _vp, _sz]),
+    "okf_gemm_gather": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, ctypes.POINTER(Gather), _vp]),
+})
+
 _lib = None
 
 

@@ -51,12 +51,16 @@ int par_flush(okf_ctx *ctx) {
                                         ctx->par_xdt, ctx->par_n, ctx->sms)) {
         e = launch_gemv_group(ctx->par_type, cnt, ctx->par_w, ctx->par_m, ctx->par_out, ctx->par_k, ctx->par_x,
                               ctx->par_xdt, ctx->par_n, ctx->dev_status, ctx->par_stream, ctx->sms, ctx->device,
-                              &ctx->launches);
+                              &ctx->launches, ctx->par_gathers ? &ctx->par_gather : nullptr);
     } else {
-        for (uint32_t i = 0; i < cnt && e == cudaSuccess; i++)
-            e = launch_gemv_fast(ctx->par_type, ctx->par_w[i], ctx->par_k, ctx->par_m[i], ctx->par_x, ctx->par_xdt,
-                                 ctx->par_n, ctx->par_out[i], ctx->dev_status, ctx->par_stream, ctx->sms,
-                                 ctx->device, &ctx->launches);
+        // one launch per matrix; with a gather each one is an exchange of its own on the set's counter
+        for (uint32_t i = 0; i < cnt && e == cudaSuccess; i++) {
+            GemvGatherPlan one = ctx->par_gather;
+            one.seg[0] = ctx->par_gather.seg[i];
+            e = launch_gemv_group(ctx->par_type, 1, &ctx->par_w[i], &ctx->par_m[i], &ctx->par_out[i], ctx->par_k,
+                                  ctx->par_x, ctx->par_xdt, ctx->par_n, ctx->dev_status, ctx->par_stream, ctx->sms,
+                                  ctx->device, &ctx->launches, ctx->par_gathers ? &one : nullptr);
+        }
     }
     return e == cudaSuccess ? OKF_OK : cuda_fail(ctx, e);
 }
@@ -78,13 +82,14 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
             if (ctx->par_open) {
                 // inside a parallel region: join the waiting matvecs if this one multiplies
                 // the same x, else send them off and start a new set
-                const bool joins = ctx->par_count > 0 && ctx->par_count < 4 && ctx->par_type == ty &&
+                const bool joins = ctx->par_count > 0 && ctx->par_count < 4 && !ctx->par_gathers && ctx->par_type == ty &&
                                    ctx->par_k == k && ctx->par_x == x && ctx->par_xdt == xdt && ctx->par_n == n &&
                                    ctx->par_stream == s;
                 if (!joins && (rc = par_flush(ctx))) return rc;
                 const uint32_t i = ctx->par_count++;
                 ctx->par_type = ty; ctx->par_k = k; ctx->par_x = x; ctx->par_xdt = xdt; ctx->par_n = n;
                 ctx->par_stream = s;
+                ctx->par_gathers = false;
                 ctx->par_w[i] = wp; ctx->par_m[i] = m; ctx->par_out[i] = (float *)out;
                 return OKF_OK;
             }
@@ -273,6 +278,113 @@ int okf_parallel_end(okf_ctx *ctx) {
     if (!ctx || !ctx->par_open) return OKF_E_ARG;
     ctx->par_open = false;
     return par_flush(ctx);
+}
+
+int okf_shared_alloc(okf_ctx *ctx, size_t bytes, void **device_ptr, okf_ipc_handle *handle) {
+    if (!ctx || !device_ptr || !handle || bytes == 0) return OKF_E_ARG;
+    static_assert(sizeof(okf_ipc_handle) >= sizeof(cudaIpcMemHandle_t), "handle too small");
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaErrorMemoryAllocation) {
+        (void)cudaGetLastError();
+        return OKF_E_NOMEM;
+    }
+    OKF_CUDA(ctx, e);
+    e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(ctx, e);
+    }
+    memset(handle, 0, sizeof(*handle));
+    memcpy(handle->bytes, &h, sizeof(h));
+    *device_ptr = p;
+    return OKF_OK;
+}
+
+int okf_shared_open(okf_ctx *ctx, const okf_ipc_handle *handle, void **device_ptr) {
+    if (!ctx || !handle || !device_ptr) return OKF_E_ARG;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle->bytes, sizeof(h));
+    // with this context's device current, the mapping also turns on peer access to the owner
+    OKF_CUDA(ctx, cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return OKF_OK;
+}
+
+int okf_shared_close(okf_ctx *ctx, void *device_ptr) {
+    if (!ctx || !device_ptr) return OKF_E_ARG;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    OKF_CUDA(ctx, cudaIpcCloseMemHandle(device_ptr));
+    return OKF_OK;
+}
+
+int okf_shared_free(okf_ctx *ctx, void *device_ptr) {
+    if (!ctx || !device_ptr) return OKF_E_ARG;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    OKF_CUDA(ctx, cudaFree(device_ptr));
+    return OKF_OK;
+}
+
+int okf_copy_to_host(okf_ctx *ctx, const void *device_ptr, void *host, size_t bytes) {
+    if (!ctx || !device_ptr || !host) return OKF_E_ARG;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    OKF_CUDA(ctx, cudaMemcpy(host, device_ptr, bytes, cudaMemcpyDeviceToHost));
+    return OKF_OK;
+}
+
+int okf_gemm_gather(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                    const void *x, int xdt, uint32_t n, const okf_gather *gt, okf_stream stream) {
+    if (!gt || gt->nranks < 2 || gt->nranks > 8 || gt->rank >= gt->nranks || !gt->epoch) return OKF_E_ARG;
+    if ((uint64_t)gt->row_first + m > gt->m_total) return OKF_E_SHAPE;
+    for (uint32_t r = 0; r < gt->nranks; r++)
+        if (!gt->out[r] || !gt->arrivals[r] || (uintptr_t)gt->out[r] % 16) return OKF_E_ARG;
+    int rc = check_gemm_args(ctx, type, w, woff, k, m, x, xdt, n, gt->out[gt->rank], DT_F32);
+    if (rc) return rc;
+    if (n > 8) return OKF_E_SHAPE;
+    const uint8_t *wp = w->dptr + woff;
+    if (!gemv_fast_supported(type, k, m, wp, x, xdt, n, ctx->sms)) return OKF_E_ALIGN;
+    if (fault_fires(ctx)) return OKF_E_INJECTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    // a set that is waiting takes this matrix in if it gathers the same way
+    const bool joins = ctx->par_open && ctx->par_count > 0 && ctx->par_count < 4 && ctx->par_gathers &&
+                       ctx->par_type == type && ctx->par_k == k && ctx->par_x == x && ctx->par_xdt == xdt &&
+                       ctx->par_n == n && ctx->par_stream == s && ctx->par_gather.nranks == gt->nranks;
+    if (ctx->par_open && !joins && (rc = par_flush(ctx))) return rc;
+    const uint32_t i = ctx->par_open ? ctx->par_count : 0;
+    GemvGatherPlan fresh = {};
+    GemvGatherPlan &plan = ctx->par_open ? ctx->par_gather : fresh;
+    if (i == 0) {  // the exchange counts on the first matrix's counter
+        plan = GemvGatherPlan{};
+        plan.nranks = gt->nranks;
+        plan.rank = gt->rank;
+        plan.epoch = gt->epoch;
+        for (uint32_t r = 0; r < gt->nranks; r++) plan.arrivals[r] = gt->arrivals[r];
+    }
+    plan.seg[i].m_total = gt->m_total;
+    plan.seg[i].row_first = gt->row_first;
+    for (uint32_t r = 0; r < gt->nranks; r++) plan.seg[i].out[r] = gt->out[r];
+    if (ctx->par_open) {
+        ctx->par_count = i + 1;
+        ctx->par_type = type; ctx->par_k = k; ctx->par_x = x; ctx->par_xdt = xdt; ctx->par_n = n;
+        ctx->par_stream = s;
+        ctx->par_gathers = true;
+        ctx->par_w[i] = wp; ctx->par_m[i] = m; ctx->par_out[i] = nullptr;
+        return OKF_OK;
+    }
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    float *none = nullptr;
+    cudaError_t e = launch_gemv_group(type, 1, &wp, &m, &none, k, x, xdt, n, ctx->dev_status, s, ctx->sms,
+                                      ctx->device, &ctx->launches, &plan);
+    return e == cudaSuccess ? OKF_OK : cuda_fail(ctx, e);
 }
 
 int okf_gemm_tile(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,

@@ -4,22 +4,23 @@
 // weight tile and a 32 x 32 activation tile for simdgroup matrices.
 //
 // Shape of the computation.  One work item is a 128-row slab of W against one
-// block of 256 tokens or, when more than 256 remain, two such blocks at once so
-// every unpacked weight tile feeds two accumulators.  Per k-block of 64:
-//   - eight warps unpack 128 rows x 64 weights to 16-bit floats and eight more
-//     copy (or convert) 256 tokens x 64 activations, both written K-major into
-//     shared memory in the 128-byte-swizzled layout the tensor core reads.
-//     Weight bytes are fetched one k-block ahead; 16-bit activations go global ->
-//     shared with asynchronous 16-byte copies that signal the stage barrier;
-//   - one thread issues four tcgen05.mma (M = 128, N = 256, K = 16) that
-//     accumulate in fp32 in tensor memory: lane = weight row, column = token;
+// block of 256 tokens or two such blocks at once, so that every unpacked weight
+// tile feeds two accumulators.  Per k-block of 64:
+//   - the activation tile(s), 256 tokens x 64 k each, come by TMA through a tensor
+//     map of X, already in the 128-byte-swizzled K-major layout the tensor core
+//     reads (fp32 activations are converted by eight warps instead);
+//   - two groups of eight warps, taking the k-blocks in turn, unpack 128 rows x 64
+//     weights to 16-bit floats into the same layout; weight bytes are fetched one
+//     turn ahead;
+//   - one thread issues four tcgen05.mma (M = 128, N = 256, K = 16) per token block
+//     that accumulate in fp32 in tensor memory: lane = weight row, column = token;
 //   - tcgen05.commit hands the stage back to the producers when the MMAs that
 //     read it are done.
 // The two 256-column accumulators of tensor memory either serve the two token
 // blocks of one item or alternate between items, so an epilogue (tcgen05.ld,
-// convert, coalesced stores along m) overlaps the next main loop.  Operands are fp16 when the activations are fp16, bf16 otherwise
-// (fp32 activations are rounded to bf16); weights are decoded exactly to fp32
-// first and rounded once.
+// convert, coalesced stores along m) overlaps the next main loop.  Operands are
+// fp16 when the activations are fp16, bf16 otherwise (fp32 activations are
+// rounded to bf16); weights are decoded exactly to fp32 first and rounded once.
 //
 // Every mbarrier wait is bounded (about a second); a wait that gives up records
 // a code in the status word, the CTA frees its tensor memory and returns.

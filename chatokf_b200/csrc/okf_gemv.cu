@@ -504,7 +504,7 @@ struct RingPos {
 };
 
 template <int TY, int XDT, bool SEP>
-__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvLayout L) {
+__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvLayout L, GemvGather G) {
     constexpr uint32_t UB = UnitGeom<TY>::bytes;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -776,11 +776,44 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
             for (int w = 0; w < kGemvWarps; w++) sum += src[(size_t)w * per_tile];
             const GemvSeg sg = gemv_segment(p, t0 + gb + tl);
             const uint32_t row = (t0 + gb + tl - sg.tile0) * 16 + r;
-            if (row < sg.m) sg.out[(size_t)col * sg.m + row] = sum;
+            if (row < sg.m) {
+                if (G.nranks == 0) {
+                    sg.out[(size_t)col * sg.m + row] = sum;
+                } else {
+                    const size_t at = (size_t)col * G.m_total[sg.index] + G.row_first[sg.index] + row;
+                    for (uint32_t rk = 0; rk < G.nranks; rk++) G.out[sg.index][rk][at] = sum;
+                }
+            }
         }
         if (gb + L.group < ntl) consumer_sync();  // before the buffer is zeroed again
     }
     OKF_GEMV_TRACE(8);
+    if (G.nranks) {
+        // the stores above must be visible on every GPU before this CTA counts itself in
+        __threadfence_system();
+        consumer_sync();
+        if (tid == 0) {
+            for (uint32_t rk = 0; rk < G.nranks; rk++) atomicAdd_system(G.arrivals[rk], 1u);
+            if (blockIdx.x == 0) {
+                // one CTA stays until every CTA of every rank has counted in here: when the
+                // launch is over, the whole output has arrived.  The wait is bounded.
+                const uint32_t e = *G.epoch + 1;
+                *G.epoch = e;
+                const uint32_t target = e * G.nranks * gridDim.x;
+                const long long t_start = clock64();
+                for (;;) {
+                    uint32_t seen;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(G.arrivals[G.rank]) : "memory");
+                    if ((int32_t)(seen - target) >= 0) break;
+                    if (clock64() - t_start > kWaitCycles) {
+                        if (p.status) atomicExch(p.status, kStatusGatherTimeout);
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+        }
+    }
 }
 
 // Shared-memory plan.  Two CTAs share an SM (this launch's and the next one's,
@@ -890,7 +923,7 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
 }
 
 template <int TY, int XDT, bool SEP>
-static cudaError_t launch_t(GemvArgs a, cudaStream_t s, int sms, int dev) {
+static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int sms, int dev) {
     GemvLayout L;
     const uint32_t ctas = a.tiles < (uint32_t)sms ? a.tiles : (uint32_t)sms;
     if (!gemv_layout(TY, a.nunit, a.n, SEP, (a.tiles + ctas - 1) / ctas, a, L)) return cudaErrorInvalidConfiguration;
@@ -911,22 +944,22 @@ static cudaError_t launch_t(GemvArgs a, cudaStream_t s, int sms, int dev) {
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<TY, XDT, SEP>, a, L);
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<TY, XDT, SEP>, a, L, G);
 }
 
 template <int TY>
-static cudaError_t launch_ty(const GemvArgs &a, int xdt, bool sep, cudaStream_t s, int sms, int dev) {
+static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bool sep, cudaStream_t s, int sms, int dev) {
     if (sep) {
         switch (xdt) {
-        case DT_F16: return launch_t<TY, DT_F16, true>(a, s, sms, dev);
-        case DT_BF16: return launch_t<TY, DT_BF16, true>(a, s, sms, dev);
-        case DT_F32: return launch_t<TY, DT_F32, true>(a, s, sms, dev);
+        case DT_F16: return launch_t<TY, DT_F16, true>(a, G, s, sms, dev);
+        case DT_BF16: return launch_t<TY, DT_BF16, true>(a, G, s, sms, dev);
+        case DT_F32: return launch_t<TY, DT_F32, true>(a, G, s, sms, dev);
         }
     } else if constexpr (TY == T_Q4_K) {
         switch (xdt) {
-        case DT_F16: return launch_t<TY, DT_F16, false>(a, s, sms, dev);
-        case DT_BF16: return launch_t<TY, DT_BF16, false>(a, s, sms, dev);
-        case DT_F32: return launch_t<TY, DT_F32, false>(a, s, sms, dev);
+        case DT_F16: return launch_t<TY, DT_F16, false>(a, G, s, sms, dev);
+        case DT_BF16: return launch_t<TY, DT_BF16, false>(a, G, s, sms, dev);
+        case DT_F32: return launch_t<TY, DT_F32, false>(a, G, s, sms, dev);
         }
     }
     return cudaErrorInvalidValue;
@@ -963,7 +996,7 @@ bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const vo
 // same type and K share every launch.
 cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, const uint32_t *m, float *const *out,
                               uint32_t k, const void *x, int xdt, uint32_t n, int *status, cudaStream_t s,
-                              int sms, int dev, uint64_t *launches) {
+                              int sms, int dev, uint64_t *launches, const GemvGatherPlan *gather) {
     if (nseg == 0 || nseg > (uint32_t)kGemvSegs) return cudaErrorInvalidValue;
     GemvArgs a = {};
     a.status = status; a.k = k;
@@ -978,6 +1011,13 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         a.tile_end[i] = tiles;
     }
     a.tiles = tiles;
+    GemvGather G = {};
+    if (gather) {
+        G.nranks = gather->nranks;
+        G.rank = gather->rank;
+        G.epoch = gather->epoch;
+        for (uint32_t r = 0; r < gather->nranks; r++) G.arrivals[r] = gather->arrivals[r];
+    }
     const size_t xsz = xdt == DT_F32 ? 4 : 2;
     for (uint32_t c0 = 0; c0 < n;) {
         const uint32_t left = n - c0;
@@ -986,15 +1026,21 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         a.x = (const uint8_t *)x + (size_t)c0 * k * xsz;
         for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {
             const uint32_t j = i < nseg ? i : nseg - 1;
-            a.out[i] = out[j] + (size_t)c0 * m[j];
+            a.out[i] = (out && out[j]) ? out[j] + (size_t)c0 * m[j] : nullptr;
+            if (gather) {
+                G.m_total[i] = gather->seg[j].m_total;
+                G.row_first[i] = gather->seg[j].row_first;
+                for (uint32_t r = 0; r < gather->nranks; r++)
+                    G.out[i][r] = gather->seg[j].out[r] + (size_t)c0 * gather->seg[j].m_total;
+            }
         }
         a.n = take;
         cudaError_t e;
         switch (ty) {
-        case T_Q4_K: e = launch_ty<T_Q4_K>(a, xdt, sep, s, sms, dev); break;
-        case T_Q8_0: e = launch_ty<T_Q8_0>(a, xdt, sep, s, sms, dev); break;
-        case T_Q2_0: e = launch_ty<T_Q2_0>(a, xdt, sep, s, sms, dev); break;
-        case T_IQ2_XXS: e = launch_ty<T_IQ2_XXS>(a, xdt, sep, s, sms, dev); break;
+        case T_Q4_K: e = launch_ty<T_Q4_K>(a, G, xdt, sep, s, sms, dev); break;
+        case T_Q8_0: e = launch_ty<T_Q8_0>(a, G, xdt, sep, s, sms, dev); break;
+        case T_Q2_0: e = launch_ty<T_Q2_0>(a, G, xdt, sep, s, sms, dev); break;
+        case T_IQ2_XXS: e = launch_ty<T_IQ2_XXS>(a, G, xdt, sep, s, sms, dev); break;
         default: e = cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) return e;
@@ -1007,7 +1053,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
 cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
                              uint32_t n, float *out, int *status, cudaStream_t s, int sms, int dev,
                              uint64_t *launches) {
-    return launch_gemv_group(ty, 1, &w, &m, &out, k, x, xdt, n, status, s, sms, dev, launches);
+    return launch_gemv_group(ty, 1, &w, &m, &out, k, x, xdt, n, status, s, sms, dev, launches, nullptr);
 }
 
 }  // namespace okf

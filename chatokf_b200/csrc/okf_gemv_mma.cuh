@@ -27,6 +27,19 @@ namespace okf {
 // Up to kGemvSegs matrices of the same type and K that multiply the same x share
 // one launch: their tiles are numbered through, segment after segment.
 constexpr int kGemvSegs = 4;
+constexpr int kMaxRanks = 8;
+// Row-sharded matrices on several GPUs: every rank stores its rows straight into
+// every rank's copy of the whole output (peer-mapped pointers), counts itself in on
+// every rank, and the launch ends on a rank only when all ranks have counted in.
+struct GemvGather {
+    uint32_t nranks;                       // 0: single GPU, `out` below is used
+    uint32_t m_total[kGemvSegs];           // rows of the whole matrix
+    uint32_t row_first[kGemvSegs];         // this rank's first row in it
+    float *out[kGemvSegs][kMaxRanks];      // rank r's [n][m_total] buffer as mapped here
+    uint32_t *arrivals[kMaxRanks];         // rank r's counter of finished CTAs, as mapped here
+    uint32_t *epoch;                       // local: exchanges started so far on this counter
+    uint32_t rank;
+};
 struct GemvArgs {
     const uint8_t *w[kGemvSegs];
     float *out[kGemvSegs];
@@ -46,13 +59,13 @@ struct GemvArgs {
 struct GemvSeg {
     const uint8_t *w;
     float *out;
-    uint32_t m, tile0, tile1;
+    uint32_t m, tile0, tile1, index;
 };
 __device__ __forceinline__ GemvSeg gemv_segment(const GemvArgs &p, uint32_t tile) {
-    GemvSeg s = {p.w[0], p.out[0], p.m[0], 0u, p.tile_end[0]};
+    GemvSeg s = {p.w[0], p.out[0], p.m[0], 0u, p.tile_end[0], 0u};
 #pragma unroll
     for (int i = 1; i < kGemvSegs; i++)
-        if (tile >= p.tile_end[i - 1]) s = {p.w[i], p.out[i], p.m[i], p.tile_end[i - 1], p.tile_end[i]};
+        if (tile >= p.tile_end[i - 1]) s = {p.w[i], p.out[i], p.m[i], p.tile_end[i - 1], p.tile_end[i], (uint32_t)i};
     return s;
 }
 
@@ -60,7 +73,7 @@ constexpr int kGemvWarps = 8;                      // consumer warps (a power of
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;  // + one producer warp
 constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
 constexpr uint32_t kSpinLimit = 1u << 16;          // polls when draining on the way out
-constexpr int kStatusFullTimeout = 1, kStatusEmptyTimeout = 2;
+constexpr int kStatusFullTimeout = 1, kStatusEmptyTimeout = 2, kStatusGatherTimeout = 4;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);

@@ -12,6 +12,8 @@ struct okf_weights {
     bool owned;
 };
 
+#include "okf_kernels.h"
+
 struct okf_ctx {
     int device;
     int sms;
@@ -42,6 +44,8 @@ struct okf_ctx {
     const uint8_t *par_w[4];
     uint32_t par_m[4];
     float *par_out[4];
+    bool par_gathers;               // the waiting set stores into every rank's output
+    okf::GemvGatherPlan par_gather;
 };
 
 

@@ -26,9 +26,22 @@ cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, c
 // one launch (per pass over columns) covers them all.
 bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
                           const void *x, int xdt, uint32_t n, int sms);
+// `gather` (may be null): the matrices are row shards of larger ones spread over
+// several GPUs; every rank stores its rows into every rank's whole output through
+// peer-mapped pointers and the launch ends when all ranks' rows have arrived
+// (bounded wait; a timeout is reported in the status word).  `out` is unused then.
+struct GemvGatherPlan {
+    uint32_t nranks, rank;
+    uint32_t *arrivals[8];  // rank r's counter, as mapped into this process
+    uint32_t *epoch;        // local device word
+    struct {
+        uint32_t m_total, row_first;
+        float *out[8];      // rank r's [n][m_total] buffer, as mapped into this process
+    } seg[4];
+};
 cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, const uint32_t *m, float *const *out,
                               uint32_t k, const void *x, int xdt, uint32_t n, int *status, cudaStream_t s,
-                              int sms, int dev, uint64_t *launches);
+                              int sms, int dev, uint64_t *launches, const GemvGatherPlan *gather);
 
 // Prefill matmul on tcgen05 / tensor memory (okf_gemm_tc.cu), any N.
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n);

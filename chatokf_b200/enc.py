@@ -176,6 +176,13 @@ class CudaEnc:
         finally:
             c._check(c.lib.okf_parallel_end(c.h), "okf_parallel_end")
 
+    def gemm_gather(self, w: GGUFTensor, X: torch.Tensor, gather, off: Weights, N: int = 1):
+        """okf_gemm_gather: this rank's rows of a row-sharded matrix, stored straight into
+        every rank's output (`gather`: a tp.PeerOutputs slot); N <= 8."""
+        c = self.ctx
+        c._check(c.lib.okf_gemm_gather(c.h, int(w.type), off.h, w.offset, w.K, w.M, X.data_ptr(), _DT[X.dtype], int(N),
+                                       ctypes.byref(gather), _stream_ptr(self.stream)), "okf_gemm_gather")
+
     def gemmTile(self, w: GGUFTensor, X: torch.Tensor, out: torch.Tensor, off: Weights, N: int):
         """MetalEnc.gemmTile: the tensor-core tile at any N (kernel bench)."""
         self._gemm(self.ctx.lib.okf_gemm_tile, "okf_gemm_tile", w, X, out, off, N)

@@ -11,6 +11,8 @@ One process per GPU; `torch.distributed` provides the process group.
 """
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 import torch
 import torch.distributed as dist
@@ -80,3 +82,93 @@ class ShardedLinear:
         if n == 1:
             return full.view(1, self.m)
         return to_token_major(full) if token_major else full
+
+
+def slot_layout(sizes: list[tuple[int, int]]) -> tuple[list[int], int]:
+    """Byte offsets of the [n][m_total] fp32 outputs in one shared buffer, each on a
+    256-byte boundary, and the buffer's size.  `sizes` holds (n, m_total) per slot."""
+    offs, at = [], 0
+    for n, m_total in sizes:
+        offs.append(at)
+        at += (n * m_total * 4 + 255) // 256 * 256
+    return offs, at
+
+
+class PeerOutputs:
+    """Output buffers of the row-sharded decode matvec that every rank's kernel writes
+    into directly (okf_gemm_gather), instead of an all-gather after the kernel.
+
+    Every rank allocates one shared buffer holding all its output slots plus one
+    arrival counter per slot, publishes the two IPC handles through the process
+    group, and maps every other rank's pair.  `slot(i, m_local)` is the okf_gather
+    record of output i for this rank's rows.  All ranks must create the object
+    with the same `sizes` and run the same sequence of gathered calls."""
+
+    def __init__(self, ctx, sizes: list[tuple[int, int]], group=None):
+        from . import _lib
+
+        self.ctx, self.group = ctx, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.sizes = list(sizes)
+        self.offs, out_bytes = slot_layout(self.sizes)
+        lib = ctx.lib
+        self._mine, handles = [], []
+        for nbytes in (out_bytes, 4 * len(sizes)):
+            p, h = ctypes.c_void_p(), _lib.IpcHandle()
+            ctx._check(lib.okf_shared_alloc(ctx.h, nbytes, ctypes.byref(p), ctypes.byref(h)), "okf_shared_alloc")
+            self._mine.append(p.value)
+            handles.append(bytes(h.bytes))
+        # the library's own word per slot: how many exchanges it has started
+        self.epochs = torch.zeros(len(sizes), dtype=torch.int32, device=f"cuda:{ctx.device}")
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, handles, group=group)
+        self._opened = []
+        self.out_base, self.cnt_base = [0] * self.world, [0] * self.world
+        for r, (h_out, h_cnt) in enumerate(everyone):
+            if r == self.rank:
+                self.out_base[r], self.cnt_base[r] = self._mine
+                continue
+            ptrs = []
+            for raw in (h_out, h_cnt):
+                h, p = _lib.IpcHandle(), ctypes.c_void_p()
+                ctypes.memmove(h.bytes, raw, 64)
+                ctx._check(lib.okf_shared_open(ctx.h, ctypes.byref(h), ctypes.byref(p)), "okf_shared_open")
+                ptrs.append(p.value)
+                self._opened.append(p.value)
+            self.out_base[r], self.cnt_base[r] = ptrs
+        self._slots = {}
+
+    def slot(self, i: int, m_local: int):
+        """okf_gather for output slot i; this rank owns rows [rank * m_local, +m_local)."""
+        from . import _lib
+
+        key = (i, m_local)
+        if key not in self._slots:
+            n, m_total = self.sizes[i]
+            g = _lib.Gather()
+            g.nranks, g.rank, g.m_total, g.row_first = self.world, self.rank, m_total, self.rank * m_local
+            for r in range(self.world):
+                g.out[r] = self.out_base[r] + self.offs[i]
+                g.arrivals[r] = self.cnt_base[r] + 4 * i
+            g.epoch = self.epochs.data_ptr() + 4 * i
+            self._slots[key] = g
+        return self._slots[key]
+
+    def read(self, i: int) -> np.ndarray:
+        """This rank's copy of output slot i as a host array [n][m_total]."""
+        n, m_total = self.sizes[i]
+        host = np.empty((n, m_total), dtype=np.float32)
+        self.ctx._check(self.ctx.lib.okf_copy_to_host(self.ctx.h, self.out_base[self.rank] + self.offs[i],
+                                                      host.ctypes.data, host.nbytes), "okf_copy_to_host")
+        return host
+
+    def close(self):
+        """Unmap the other ranks' buffers, then (after a barrier) free this rank's."""
+        lib = self.ctx.lib
+        for p in self._opened:
+            lib.okf_shared_close(self.ctx.h, p)
+        self._opened = []
+        dist.barrier(group=self.group)
+        for p in self._mine:
+            lib.okf_shared_free(self.ctx.h, p)
+        self._mine = []

@@ -121,6 +121,43 @@ OKF_API int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff
 OKF_API int okf_parallel_begin(okf_ctx *ctx);
 OKF_API int okf_parallel_end(okf_ctx *ctx);
 
+/* ---- row shards on several GPUs -------------------------------------------------
+ * The reference runs on one GPU and has no counterpart for this block.  A matrix
+ * is cut by output rows, rank r holding rows [row_first, row_first + M) of
+ * m_total; every rank computes its rows and the whole output is needed on every
+ * rank.  okf_gemm_gather does both in one kernel: each rank stores its rows
+ * straight into every rank's copy of the output (pointers mapped from the other
+ * processes, plain stores over NVLink) and counts itself in on every rank; the
+ * launch on a rank ends when all ranks have counted in there, so whatever follows
+ * it on the stream sees the whole output.  That wait is bounded (about a
+ * second): if a rank never arrives, the launch ends anyway and
+ * okf_device_status reports 4.
+ *
+ * Buffers other ranks write into come from okf_shared_alloc (zero-filled), whose
+ * handle another process on the same machine turns into a pointer with
+ * okf_shared_open.  All ranks must issue the same sequence of calls with the same
+ * shapes.  N <= 8 and fp32 outputs only (the matmul for more tokens gathers with
+ * a collective).  A buffer must not be written by the next exchange while a rank
+ * may still read the previous one: alternate two buffers or order the work. */
+typedef struct okf_ipc_handle { unsigned char bytes[64]; } okf_ipc_handle;
+typedef struct okf_gather {
+    uint32_t nranks;         /* 2..8 */
+    uint32_t rank;           /* this process */
+    uint32_t m_total;        /* rows of the whole matrix */
+    uint32_t row_first;      /* first of this rank's rows */
+    float *out[8];           /* rank r's [N][m_total] output, as mapped into this process */
+    uint32_t *arrivals[8];   /* rank r's arrival counter for this matrix (4 bytes, shared), as mapped here */
+    uint32_t *epoch;         /* 4 bytes of this rank's own device memory, zero at start, used by the library */
+} okf_gather;
+OKF_API int okf_shared_alloc(okf_ctx *ctx, size_t bytes, void **device_ptr, okf_ipc_handle *handle);
+OKF_API int okf_shared_open(okf_ctx *ctx, const okf_ipc_handle *handle, void **device_ptr);
+OKF_API int okf_shared_close(okf_ctx *ctx, void *device_ptr);
+OKF_API int okf_shared_free(okf_ctx *ctx, void *device_ptr);
+/* Synchronous device -> host copy of `bytes` (for reading shared buffers back). */
+OKF_API int okf_copy_to_host(okf_ctx *ctx, const void *device_ptr, void *host, size_t bytes);
+OKF_API int okf_gemm_gather(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                            const void *x, int xdt, uint32_t n, const okf_gather *g, okf_stream stream);
+
 /* Same contract as okf_gemm but always the tensor-core tile, whatever N is.
  * Replaces MetalEnc.gemmTile (Base/MetalEnc.swift:326-352), which the
  * reference's kernel bench uses to time the tile at small N. */

@@ -74,3 +74,13 @@ def test_token_major_layout():
     t = tp.to_token_major(g)
     assert t.shape == (3, 8)
     assert t[1].tolist() == [4, 5, 6, 7, 16, 17, 18, 19]
+
+
+def test_slot_layout_of_shared_outputs():
+    """Outputs that other ranks write into share one buffer: 256-byte aligned slots."""
+    from chatokf_b200.tp import slot_layout
+
+    offs, total = slot_layout([(1, 9728), (1, 9728), (4, 2560), (1, 3)])
+    assert offs == [0, 38912, 77824, 118784]
+    assert total == 118784 + 256
+    assert all(o % 256 == 0 for o in offs)
