@@ -201,6 +201,28 @@ template <> struct ARaw<T_Q4_K> {
         }
     }
 };
+template <> struct ARaw<T_Q8_0> {
+    uint32_t w[10], sh;  // the 34-byte block {f16 d; i8 q[32]} and what precedes it in its first word
+    __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) {
+        const uint8_t *b = row + (size_t)(kb * 2 + h) * 34;  // 2-byte aligned
+        const uint32_t *p = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(b) & ~(uintptr_t)3);
+        sh = ((uint32_t)reinterpret_cast<uintptr_t>(b) & 2u) * 8u;
+#pragma unroll
+        for (int i = 0; i < 10; i++) w[i] = __ldg(p + i);  // may run a few bytes past the block (buffers are padded)
+    }
+    __device__ __forceinline__ void decode(float (&v)[32], const uint64_t *) const {
+        uint32_t u[9];
+#pragma unroll
+        for (int i = 0; i < 9; i++) u[i] = __funnelshift_r(w[i], w[i + 1], sh);
+        const float d = f16bits(u[0] & 0xFFFF);
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const int at = 2 + j;  // byte index in the block
+            const uint32_t word = u[at >> 2] ^ 0x80808080u;  // q + 128 as an unsigned byte
+            v[j] = d * (byte_to_f32(word, at & 3) - 128.f);
+        }
+    }
+};
 template <> struct ARaw<T_Q2_0> {
     uint32_t c0, c1, dbits;  // 32 two-bit codes and the block scale
     __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) {
