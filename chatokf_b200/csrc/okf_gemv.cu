@@ -14,22 +14,23 @@
 // of tiles the slots are summed in warp order and stored, so results do not
 // depend on timing.
 //
-// Activations.  Each 32-wide block of a column of x is reduced to 16-bit
-// integers with one fp32 scale, x ~ xs * q, |q| <= 32512 (round to nearest; the
-// step is 2^-15 of the block's largest magnitude), and q is split into two
-// signed bytes, q = 256 * hi + lo.  Every kernel here works on these values, so
-// one column gives the same result whatever the batch width.
+// Activations.  Each 256-wide unit of a column of x is reduced to 16-bit integers
+// with one fp32 scale, x ~ xs * q, |q| <= 32512 (round to nearest; the step is
+// 2^-15 of the unit's largest magnitude), and q is split into two signed bytes,
+// q = 256 * hi + lo.  Every kernel here works on these values, so one column
+// gives the same result whatever the batch width.
 //
-// One column ("SEP", integer tensor cores).  Weights go into the MMA as the
-// bytes they are stored as (nibbles and 2-bit codes after one AND, Q8_0 and
-// the IQ2_XXS codebook untouched), x as the hi / lo bytes, mma.sync m16n8k32
-// with s32 accumulators: the sums are exact integers.  MMA column g stands for
-// (quarter g / 2 of the unit, byte g % 2 of x).  Thread c of a quad owns the k
-// of quarter c and feeds x only into that quarter's columns, so the accumulator
-// a thread reads back is the sum over exactly the 64 k whose block scales it
-// decoded; scales, mins and biases are applied in fp32.  More columns are run
-// as one pass per column, except for Q4_K, which has a variant for four
-// columns per pass ("PRE", fp16 tensor cores, x = hi + lo in fp16).
+// Integer tensor cores.  Weights go into the MMA as the bytes they are stored as
+// (nibbles and 2-bit codes after one AND, Q8_0 and the IQ2_XXS codebook
+// untouched), x as the hi / lo bytes, mma.sync m16n8k32 with s32 accumulators:
+// the sums are exact integers; scales, mins and biases are applied afterwards.
+//   One column ("SEP"): MMA column g stands for (quarter g / 2 of the unit, byte
+// g % 2 of x).  Thread c of a quad owns the k of quarter c and feeds x only into
+// that quarter's columns, so the accumulator a thread reads back is the sum over
+// exactly the 64 k whose block scales it decoded.
+//   Two to four columns ("WIDE"): MMA column g stands for (activation column g / 2,
+// byte g % 2); one MMA per 32-wide block, fed by all four threads of the quad.
+// More than four columns are run as passes.
 #include "okf_gemv_mma.cuh"
 #include "okf_kernels.h"
 
@@ -50,17 +51,16 @@ struct GemvLayout {
     uint32_t ragged;       // mode 2: row segments do not start on 16-byte boundaries
     uint32_t group;        // tiles summed per barrier
     uint32_t nc;           // real activation columns of this pass
-    uint32_t ecols;        // columns of the x panel in shared memory (SEP: hi, lo bytes; PRE: 4 hi + 4 lo)
+    uint32_t ecols;        // byte columns of the x panel in shared memory: hi and lo of every activation column
     uint32_t es;           // bytes between columns of the x panel
     uint32_t panel;        // k-chunks whose slice of x is staged together
-    uint32_t xs_off, info_off, red_off, zero_off, tab_off;  // byte offsets in dynamic shared memory
+    uint32_t xs_off, info_off, red_off, tab_off;  // byte offsets in dynamic shared memory
     uint32_t smem_bytes;
 };
 
 constexpr uint32_t kBarBytes = 256;
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kConsumers = kGemvWarps * 32;
-constexpr uint32_t kZeroBytes = 3 * 144 + 64 + 128;  // PRE: a column's worth of zeros for idle MMA columns
 // SEP x panel: a unit of a byte column is its 256 bytes in k order, except that
 // in quarters 2 and 3 neighbouring 16-byte pieces are swapped; with the second
 // byte column 32 (mod 128) bytes after the first, the eight lanes of a load that
@@ -287,48 +287,123 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
     }
 }
 
-// ---- per-unit arithmetic, Q4_K with up to eight columns ("PRE") ---------------
-// The 6-bit scale is multiplied into the fp16 nibbles (exact: <= 945 * 2^-24), the
-// eight sub-block sums share one accumulator, and a second MMA chain with the
-// 6-bit mins in place of the weights gives the min term.
-__device__ __forceinline__ void unit_q4k_pre(const uint8_t *ua, const uint8_t *ub, uint32_t c,
-                                             const uint32_t (&xf)[32], float (&acc)[4]) {
-    const uint4 ha = lds128(ua), hb = lds128(ub);
-    const uint4 a0 = lds128(ua + 16 + 32 * c), a1 = lds128(ua + 32 + 32 * c);
-    const uint4 b0 = lds128(ub + 16 + 32 * c), b1 = lds128(ub + 32 + 32 * c);
-    const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-    uint32_t sca, mna, scb, mnb;
-    q4k_scale_min(ha, c, sca, mna);
-    q4k_scale_min(hb, c, scb, mnb);
-    const uint32_t sa_lo = h2_bcast(byte_to_f32(sca, 0)), sa_hi = h2_bcast(byte_to_f32(sca, 1) * 0.0625f);
-    const uint32_t sb_lo = h2_bcast(byte_to_f32(scb, 0)), sb_hi = h2_bcast(byte_to_f32(scb, 1) * 0.0625f);
-    const uint32_t ma_lo = h2_bcast(byte_to_f32(mna, 0)), ma_hi = h2_bcast(byte_to_f32(mna, 1));
-    const uint32_t mb_lo = h2_bcast(byte_to_f32(mnb, 0)), mb_hi = h2_bcast(byte_to_f32(mnb, 1));
-    float cf0[4] = {0.f, 0.f, 0.f, 0.f}, cf1[4] = {0.f, 0.f, 0.f, 0.f};
-    float cm0[4] = {0.f, 0.f, 0.f, 0.f}, cm1[4] = {0.f, 0.f, 0.f, 0.f};
+// ---- per-unit arithmetic, up to four columns ("WIDE") ---------------------------
+// MMA column g stands for (activation column g / 2, byte g % 2 of x); all four
+// threads of a quad feed every MMA, thread c with the eight k [8c, 8c + 8) of a
+// 32-wide block (Q2_0: k = 16w + 4b + c for word w, byte b).  One MMA per block:
+// what comes back to thread (g, c) is the block's integer sum for rows g, g + 8
+// and activation column c, hi and lo byte.  Block scales multiply these sums as
+// integers where they are integers (Q4_K), else in fp32.
+// xf: this thread's 64 bytes of x for the unit, block b in xf[2b], xf[2b+1].
+// xw: {xs, -, -, -, X0..X7}: the unit's scale for column c and the integer sums
+// of x over its eight blocks.  acc: rows g, g + 8 of column c.
+__device__ __forceinline__ uint2 lds64(const uint8_t *p) { return *reinterpret_cast<const uint2 *>(p); }
+__device__ __forceinline__ int ubyte(uint32_t v, int i) { return (int)__byte_perm(v, 0, 0x4440 + i); }
+
+template <int TY>
+__device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, uint32_t c, const uint32_t (&xf)[16],
+                                          const float *xw, const uint2 *tab, float (&acc)[2]) {
+    const float xs = xw[0];
+    if constexpr (TY == T_Q4_K) {
+        const uint4 ha = lds128(ua), hb = lds128(ub);
+        // 6-bit scales and mins of the eight sub-blocks, four to a word (get_scale_min_k4)
+        const uint32_t sa03 = ha.y & 0x3F3F3F3Fu, ma03 = ha.z & 0x3F3F3F3Fu;
+        const uint32_t sa47 = (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u);
+        const uint32_t ma47 = ((ha.w >> 4) & 0x0F0F0F0Fu) | ((ha.z >> 2) & 0x30303030u);
+        const uint32_t sb03 = hb.y & 0x3F3F3F3Fu, mb03 = hb.z & 0x3F3F3F3Fu;
+        const uint32_t sb47 = (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u);
+        const uint32_t mb47 = ((hb.w >> 4) & 0x0F0F0F0Fu) | ((hb.z >> 2) & 0x30303030u);
+        const int4 x03 = *reinterpret_cast<const int4 *>(xw + 4), x47 = *reinterpret_cast<const int4 *>(xw + 8);
+        const int xb[8] = {x03.x, x03.y, x03.z, x03.w, x47.x, x47.y, x47.z, x47.w};
+        const uint32_t ml = 0x0F0F0F0Fu, mh = 0xF0F0F0F0u;
+        int te[4] = {0, 0, 0, 0}, to[4] = {0, 0, 0, 0};  // sum of scale * block sum: low-nibble / high-nibble blocks
+        int mina = 0, minb = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const uint32_t ta = wa[i] >> 8, tb = wb[i] >> 8;
-        mma_f16(cf0, hmul2_u(wa[i] & 0x000F000Fu, sa_lo), hmul2_u(wb[i] & 0x000F000Fu, sb_lo),
-                hmul2_u(ta & 0x000F000Fu, sa_lo), hmul2_u(tb & 0x000F000Fu, sb_lo), xf[2 * i], xf[2 * i + 1]);
-        mma_f16(cm0, ma_lo, mb_lo, ma_lo, mb_lo, xf[2 * i], xf[2 * i + 1]);
-        mma_f16(cf1, hmul2_u(wa[i] & 0x00F000F0u, sa_hi), hmul2_u(wb[i] & 0x00F000F0u, sb_hi),
-                hmul2_u(ta & 0x00F000F0u, sa_hi), hmul2_u(tb & 0x00F000F0u, sb_hi), xf[16 + 2 * i], xf[16 + 2 * i + 1]);
-        mma_f16(cm1, ma_hi, mb_hi, ma_hi, mb_hi, xf[16 + 2 * i], xf[16 + 2 * i + 1]);
+        for (int p = 0; p < 4; p++) {  // 32 bytes of nibbles: block 2p in the low ones, 2p+1 in the high ones
+            const uint2 wa = lds64(ua + 16 + 32 * p + 8 * c), wb = lds64(ub + 16 + 32 * p + 8 * c);
+            const int sa0 = ubyte(p < 2 ? sa03 : sa47, (2 * p) & 3), sa1 = ubyte(p < 2 ? sa03 : sa47, (2 * p + 1) & 3);
+            const int sb0 = ubyte(p < 2 ? sb03 : sb47, (2 * p) & 3), sb1 = ubyte(p < 2 ? sb03 : sb47, (2 * p + 1) & 3);
+            int d[4];
+            imma0<false>(d, wa.x & ml, wb.x & ml, wa.y & ml, wb.y & ml, xf[4 * p], xf[4 * p + 1]);
+            te[0] += sa0 * d[0]; te[1] += sa0 * d[1]; te[2] += sb0 * d[2]; te[3] += sb0 * d[3];
+            imma0<false>(d, wa.x & mh, wb.x & mh, wa.y & mh, wb.y & mh, xf[4 * p + 2], xf[4 * p + 3]);
+            to[0] += sa1 * d[0]; to[1] += sa1 * d[1]; to[2] += sb1 * d[2]; to[3] += sb1 * d[3];
+            mina += ubyte(p < 2 ? ma03 : ma47, (2 * p) & 3) * xb[2 * p] + ubyte(p < 2 ? ma03 : ma47, (2 * p + 1) & 3) * xb[2 * p + 1];
+            minb += ubyte(p < 2 ? mb03 : mb47, (2 * p) & 3) * xb[2 * p] + ubyte(p < 2 ? mb03 : mb47, (2 * p + 1) & 3) * xb[2 * p + 1];
+        }
+        const float da = f16bits(ha.x & 0xFFFF), dma = f16bits(ha.x >> 16);
+        const float db = f16bits(hb.x & 0xFFFF), dmb = f16bits(hb.x >> 16);
+        // The scaled sums no longer fit 256 * hi + lo in 32 bits: join them in fp32.  The
+        // high-nibble sums are exact multiples of 16, taken out by a shift; everything
+        // converted is below 2^24 in magnitude.
+        auto join = [](int hi, int lo) { return fmaf((float)hi, 256.f, (float)lo); };
+        acc[0] += xs * (da * (join(te[0], te[1]) + join(to[0] >> 4, to[1] >> 4)) - dma * (float)mina);
+        acc[1] += xs * (db * (join(te[2], te[3]) + join(to[2] >> 4, to[3] >> 4)) - dmb * (float)minb);
+    } else if constexpr (TY == T_Q8_0) {
+        float fa = 0.f, fb = 0.f;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {  // block b: {f16 d; i8 q[32]}, this thread's quants at 2 + 8c
+            uint32_t qa[2], qb[2];
+            lds_a2<2>(ua + 34 * b + 2 + 8 * c, qa);
+            lds_a2<2>(ub + 34 * b + 2 + 8 * c, qb);
+            int d[4];
+            imma0<true>(d, qa[0], qb[0], qa[1], qb[1], xf[2 * b], xf[2 * b + 1]);
+            fa += f16bits(ld_u16(ua + 34 * b)) * join_hi_lo(d[0], d[1]);
+            fb += f16bits(ld_u16(ub + 34 * b)) * join_hi_lo(d[2], d[3]);
+        }
+        acc[0] += xs * fa;
+        acc[1] += xs * fb;
+    } else if constexpr (TY == T_Q2_0) {
+        const int4 x03 = *reinterpret_cast<const int4 *>(xw + 4), x47 = *reinterpret_cast<const int4 *>(xw + 8);
+        const int xsum[2] = {x03.x + x03.y + x03.z + x03.w, x47.x + x47.y + x47.z + x47.w};
+        float fa = 0.f, fb = 0.f;
+#pragma unroll
+        for (int blk = 0; blk < 2; blk++) {  // block of 128 codes: {f16 d; u8 qs[32]}
+            const uint8_t *pa = ua + 34 * blk, *pb = ub + 34 * blk;
+            int t[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int sb = 0; sb < 4; sb++) {  // 8 bytes = 32 codes; this thread takes code c of every byte
+                uint32_t wa[2], wb[2];
+                lds_a2<2>(pa + 2 + 8 * sb, wa);
+                lds_a2<2>(pb + 2 + 8 * sb, wb);
+                const uint32_t m = 0x03030303u, sh = 2 * c;
+                int d[4];
+                imma0<false>(d, (wa[0] >> sh) & m, (wb[0] >> sh) & m, (wa[1] >> sh) & m, (wb[1] >> sh) & m,
+                             xf[8 * blk + 2 * sb], xf[8 * blk + 2 * sb + 1]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) t[e] += d[e];
+            }
+            // (code - 1) * d: the sum of x over the block leaves again
+            fa += f16bits(ld_u16(pa)) * (join_hi_lo(t[0], t[1]) - (float)xsum[blk]);
+            fb += f16bits(ld_u16(pb)) * (join_hi_lo(t[2], t[3]) - (float)xsum[blk]);
+        }
+        acc[0] += xs * fa;
+        acc[1] += xs * fb;
+    } else {
+        // IQ2_XXS: codebook entry c of every sub-block is this thread's eight weights
+        const uint2 *sgn = tab + 256;
+        float fa = 0.f, fb = 0.f;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            uint32_t wa[2], wb[2];  // a0: four codebook indices, a1: four 7-bit sign indices + 4-bit scale
+            lds_a2<2>(ua + 2 + 8 * b, wa);
+            lds_a2<2>(ub + 2 + 8 * b, wb);
+            const uint2 ea = tab[(wa[0] >> (8 * c)) & 0xFF], eb = tab[(wb[0] >> (8 * c)) & 0xFF];
+            const uint2 ma = sgn[(wa[1] >> (7 * c)) & 127u], mb = sgn[(wb[1] >> (7 * c)) & 127u];
+            int pos[4], neg[4];
+            imma0<false>(pos, ea.x, eb.x, ea.y, eb.y, xf[2 * b], xf[2 * b + 1]);
+            imma0<false>(neg, ea.x & ma.x, eb.x & mb.x, ea.y & ma.y, eb.y & mb.y, xf[2 * b], xf[2 * b + 1]);
+            fa += (0.5f + (float)(wa[1] >> 28)) * join_hi_lo(pos[0] - 2 * neg[0], pos[1] - 2 * neg[1]);
+            fb += (0.5f + (float)(wb[1] >> 28)) * join_hi_lo(pos[2] - 2 * neg[2], pos[3] - 2 * neg[3]);
+        }
+        acc[0] += xs * 0.25f * f16bits(ld_u16(ua)) * fa;
+        acc[1] += xs * 0.25f * f16bits(ld_u16(ub)) * fb;
     }
-    const float da = f16bits(ha.x & 0xFFFF), dma = f16bits(ha.x >> 16);
-    const float db = f16bits(hb.x & 0xFFFF), dmb = f16bits(hb.x >> 16);
-    const float fa = da * 16777216.f, fb = db * 16777216.f;
-    acc[0] += fa * (cf0[0] + cf1[0]) - dma * (cm0[0] + cm1[0]);
-    acc[1] += fa * (cf0[1] + cf1[1]) - dma * (cm0[1] + cm1[1]);
-    acc[2] += fb * (cf0[2] + cf1[2]) - dmb * (cm0[2] + cm1[2]);
-    acc[3] += fb * (cf0[3] + cf1[3]) - dmb * (cm0[3] + cm1[3]);
 }
 
 // ---- staging x ------------------------------------------------------------------
-// One item is 16 consecutive k of one column; two neighbouring items (lanes)
-// make one 32-wide block and agree on its scale.
+// One item is 16 consecutive k of one column; the 16 neighbouring items (lanes) of
+// a 256-wide unit agree on its scale, two neighbours make one 32-wide block.
 template <int XDT> struct XRaw { uint4 v[XDT == DT_F32 ? 4 : 2]; };
 
 template <int XDT>
@@ -341,9 +416,9 @@ __device__ __forceinline__ XRaw<XDT> load16(const void *x, size_t src, bool live
     return r;
 }
 
-// The 16 integers, the block's scale (NaN if the block holds a NaN, so that it
-// spreads to the results as it would in a plain dot product) and the block's
-// integer sum.
+// The 16 integers, the unit's scale (NaN if the unit holds a NaN, so that it
+// spreads to the results as it would in a plain dot product) and the 32-wide
+// block's integer sum.
 template <int XDT>
 __device__ __forceinline__ void quantize16(const XRaw<XDT> &raw, int (&q)[16], float &xs, int &qsum) {
     float v[16];
@@ -369,12 +444,13 @@ __device__ __forceinline__ void quantize16(const XRaw<XDT> &raw, int (&q)[16], f
             }
         }
     }
-    // largest magnitude; a NaN anywhere makes the sum of squares-free test below fail
+    // largest magnitude of the 256-wide unit (16 neighbouring items); a NaN anywhere
+    // makes the probe below a NaN
     float m8[8], bad8[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         m8[j] = fmaxf(fabsf(v[j]), fabsf(v[j + 8]));
-        bad8[j] = v[j] + v[j + 8];  // NaN if either is (inf - inf cannot occur: same-block infs give NaN results anyway)
+        bad8[j] = v[j] + v[j + 8];  // NaN if either is (inf - inf cannot matter: infs give NaN results anyway)
     }
 #pragma unroll
     for (int w = 4; w >= 1; w >>= 1)
@@ -383,8 +459,12 @@ __device__ __forceinline__ void quantize16(const XRaw<XDT> &raw, int (&q)[16], f
             m8[j] = fmaxf(m8[j], m8[j + w]);
             bad8[j] = bad8[j] + bad8[j + w];
         }
-    float amax = fmaxf(m8[0], __shfl_xor_sync(0xffffffffu, m8[0], 1));
-    const float nanprobe = bad8[0] + __shfl_xor_sync(0xffffffffu, bad8[0], 1);
+    float amax = m8[0], nanprobe = bad8[0];
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        nanprobe += __shfl_xor_sync(0xffffffffu, nanprobe, o);
+    }
     const bool bad = nanprobe != nanprobe && !(amax == __int_as_float(0x7F800000));
     const float inv = amax > 0.f ? __fdividef(kXqMax, amax) : 0.f;  // an infinite amax gives 0 and xs = inf
     xs = bad ? __int_as_float(0x7FC00000) : amax * (1.f / kXqMax);
@@ -447,43 +527,63 @@ __device__ __forceinline__ void stage_x_bytes(uint8_t *xs, float4 *info, const G
     }
 }
 
-// PRE: up to four columns as fp16 pairs hi + lo of xs * q (columns j and 4 + j
-// of the panel), in the register order the unit code expects: register
-// 2r + (j & 1) of a 16-k item = (x[4r + j], x[4r + j + 2]).
-template <int XDT>
-__device__ __forceinline__ void stage_x_halves(uint8_t *xs, const GemvLayout &L, const void *x, uint32_t kdim,
-                                               uint32_t u_first, uint32_t nu, uint32_t tid) {
+// WIDE: up to four columns, each as a hi and a lo byte column (panel columns 2j and
+// 2j + 1).  Inside a unit of a byte column, thread c's 64 bytes start at 64c: eight
+// bytes per 32-wide block, block after block, the 16-byte pieces of threads 2 and 3
+// swapped in pairs as in the one-column panel.  The eight bytes of a block are its
+// k [8c, 8c + 8) in order (Q2_0: k = 16w + 4b + c for word w, byte b).
+// xw[(unit * 4 + column) * 12]: {xs, -, -, -, X0 .. X7}.
+template <int TY, int XDT>
+__device__ __forceinline__ void stage_x_wide(uint8_t *xs, float *xw, const GemvLayout &L, const void *x, uint32_t kdim,
+                                             uint32_t u_first, uint32_t nu, uint32_t tid) {
     const uint32_t items_per_col = nu * 16;
     const uint32_t total = (L.nc * items_per_col + 31) & ~31u;
     for (uint32_t i = tid; i < total; i += kConsumers) {
         const bool live = i < L.nc * items_per_col;
         const uint32_t col = live ? i / items_per_col : 0, it = live ? i % items_per_col : 0;
-        const uint32_t u = it >> 4, c = (it >> 2) & 3, piece = it & 3;
+        const uint32_t u = it >> 4, blk = (it >> 1) & 7, half = it & 1;  // unit, 32-wide block, 16-k half of it
         int q[16], qsum;
         float scale;
-        quantize16<XDT>(load16<XDT>(x, (size_t)col * kdim + (size_t)(u_first + u) * 256 + c * 64 + piece * 16, live), q, scale,
+        quantize16<XDT>(load16<XDT>(x, (size_t)col * kdim + (size_t)(u_first + u) * 256 + (it & 15) * 16, live), q, scale,
                         qsum);
         if (!live) continue;
-        float hi[16], lo[16];
+        uint8_t *base = xs + (2 * col) * L.es + u * kXqUnit;
+        if constexpr (TY == T_Q2_0) {
+            // k = 16 * half + 4 * b + c: thread c gets four bytes (b = 0..3) from this item
 #pragma unroll
-        for (int j = 0; j < 16; j++) {
-            const float v = scale * (float)q[j];
-            hi[j] = __half2float(__float2half_rn(v));
-            lo[j] = v - hi[j];
-        }
-        uint32_t rh[8], rl[8];
+            for (int c = 0; c < 4; c++) {
+                uint32_t t[4];
 #pragma unroll
-        for (int r = 0; r < 8; r++) {
-            const int k0 = 4 * (r >> 1) + (r & 1), k1 = k0 + 2;
-            rh[r] = pack_h2(hi[k0], hi[k1]);
-            rl[r] = pack_h2(lo[k0], lo[k1]);
+                for (int b = 0; b < 4; b++) t[b] = (uint32_t)(q[4 * b + c] + 128);
+                const uint32_t h = __byte_perm(__byte_perm(t[0], t[1], 0x0051), __byte_perm(t[2], t[3], 0x0051), 0x5410);
+                const uint32_t l = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410) ^ 0x80808080u;
+                uint8_t *dst = base + xq_piece_offset(c, blk >> 1) + (blk & 1) * 8 + half * 4;
+                *reinterpret_cast<uint32_t *>(dst) = h;
+                *reinterpret_cast<uint32_t *>(dst + L.es) = l;
+            }
+        } else {
+            // k = 16 * half + 0..15: threads 2 * half and 2 * half + 1 get eight bytes each
+#pragma unroll
+            for (int cc = 0; cc < 2; cc++) {
+                uint32_t h[2], l[2];
+#pragma unroll
+                for (int w = 0; w < 2; w++) {
+                    uint32_t t[4];
+#pragma unroll
+                    for (int b = 0; b < 4; b++) t[b] = (uint32_t)(q[8 * cc + 4 * w + b] + 128);
+                    h[w] = __byte_perm(__byte_perm(t[0], t[1], 0x0051), __byte_perm(t[2], t[3], 0x0051), 0x5410);
+                    l[w] = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410) ^ 0x80808080u;
+                }
+                uint8_t *dst = base + xq_piece_offset(2 * half + cc, blk >> 1) + (blk & 1) * 8;
+                *reinterpret_cast<uint2 *>(dst) = make_uint2(h[0], h[1]);
+                *reinterpret_cast<uint2 *>(dst + L.es) = make_uint2(l[0], l[1]);
+            }
         }
-        uint8_t *dst = xs + col * L.es + u * kXsUnit + c * 144 + piece * 32;
-        *reinterpret_cast<uint4 *>(dst) = make_uint4(rh[0], rh[1], rh[2], rh[3]);
-        *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(rh[4], rh[5], rh[6], rh[7]);
-        uint8_t *dl = dst + (size_t)4 * L.es;
-        *reinterpret_cast<uint4 *>(dl) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
-        *reinterpret_cast<uint4 *>(dl + 16) = make_uint4(rl[4], rl[5], rl[6], rl[7]);
+        float *w12 = xw + ((size_t)u * 4 + col) * 12;
+        if (half == 0) {
+            reinterpret_cast<int *>(w12)[4 + blk] = qsum;
+            if (blk == 0) w12[0] = scale;
+        }
     }
 }
 
@@ -512,9 +612,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kMaxStages);
     uint8_t *stages = smem + kBarBytes;
     uint8_t *xs = smem + L.xs_off;
-    float4 *info = reinterpret_cast<float4 *>(smem + L.info_off);  // SEP: [unit][quarter]
+    float4 *info = reinterpret_cast<float4 *>(smem + L.info_off);  // SEP: [unit][quarter]; WIDE: [unit][column] x 3
     float *red = reinterpret_cast<float *>(smem + L.red_off);      // [tile in group][warp][16][nc]
-    uint8_t *zeros = smem + L.zero_off;
     const uint2 *tab = reinterpret_cast<const uint2 *>(smem + L.tab_off);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
@@ -631,23 +730,12 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     auto consumer_sync = [&]() { named_bar_sync(1, kConsumers); };
 
     // What this thread feeds into column g of the MMA's B operand.
-    //   SEP: byte column g % 2 of x, and only in the lanes of quarter g / 2.
-    //   PRE: column g of the panel (hi halves of columns 0..3, then their lo halves);
-    //        threads with nothing to feed read a block of zeros laid out like a column.
-    bool x_active;
-    const uint8_t *xs_mine;
-    uint32_t xs_ustride;
-    if constexpr (SEP) {
-        x_active = (g >> 1) == c;
-        xs_mine = xs + (g & 1) * L.es + c * 64;
-        xs_ustride = kXqUnit;
-    } else {
-        x_active = (g & 3) < p.n;
-        xs_mine = x_active ? xs + g * L.es + c * 144 : zeros + c * 144 + (g & 1) * 64;
-        xs_ustride = x_active ? kXsUnit : 0;
-        if (tid < kZeroBytes / 4) reinterpret_cast<uint32_t *>(zeros)[tid] = 0u;
-    }
-
+    //   SEP:  byte column g % 2 of x, and only in the lanes of quarter g / 2.
+    //   WIDE: byte column g of the panel (hi, lo of activation column g / 2), every lane
+    //         its own 64 bytes; lanes of columns past the last one feed zeros.
+    const bool x_active = SEP ? (g >> 1) == c : g < 2 * p.n;
+    const uint8_t *xs_mine = xs + (SEP ? (g & 1) : g) * L.es + c * 64;
+    const uint32_t xs_ustride = kXqUnit;
     const uint32_t xq_swap = (c >> 1) * 16;
     RingPos rp;
     uint32_t rot = 0;  // the deal of units to warps rotates from step to step
@@ -661,7 +749,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                 // the previous panel is still being read until every warp gets here
                 if (gb > 0 || j0 > 0) consumer_sync();
                 if constexpr (SEP) stage_x_bytes<TY, XDT>(xs, info, L, p.x, pu0, pnu, tid);
-                else stage_x_halves<XDT>(xs, L, p.x, p.k, pu0, pnu, tid);
+                else stage_x_wide<TY, XDT>(xs, reinterpret_cast<float *>(info), L, p.x, p.k, pu0, pnu, tid);
             }
             consumer_sync();
             OKF_GEMV_TRACE(4);
@@ -731,28 +819,28 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                             }
                             if (c < 2) dst[g + 8 * c] += c ? acc[1] : acc[0];
                         } else {
-                            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                            float acc[2] = {0.f, 0.f};
                             do {
-                                uint32_t xf[32];
-                                const uint4 *xp = reinterpret_cast<const uint4 *>(xs_mine + (pu + u) * xs_ustride);
+                                uint32_t xf[16];
+                                const uint8_t *xp = xs_mine + (pu + u) * xs_ustride;
 #pragma unroll
-                                for (int q = 0; q < 8; q++) {
-                                    const uint4 w4 = xp[q];
+                                for (int q = 0; q < 4; q++) {
+                                    uint4 w4 = make_uint4(0u, 0u, 0u, 0u);
+                                    if (x_active) w4 = lds128(xp + (q >> 1) * 32 + ((q & 1) ? 16 - xq_swap : xq_swap));
                                     xf[4 * q] = w4.x; xf[4 * q + 1] = w4.y; xf[4 * q + 2] = w4.z; xf[4 * q + 3] = w4.w;
                                 }
                                 const uint32_t off = (ubase + u) * UB;
-                                unit_q4k_pre(ta + off, tb + off, c, xf, acc);
+                                // lanes of columns that do not exist read column 0's record; their sums are dropped
+                                const float *xw = reinterpret_cast<const float *>(info) + ((size_t)(pu + u) * 4 + (c < L.nc ? c : 0)) * 12;
+                                unit_wide<TY>(ta + off, tb + off, c, xf, xw, tab, acc);
                                 v += kGemvWarps;
                                 u += kGemvWarps;
                                 while (u >= nu && v < total) { u -= nu; ti++; }
                             } while (v < total && ti == cur);
-                            // columns 4..7 hold the lo halves of columns 0..3
-#pragma unroll
-                            for (int e = 0; e < 4; e++) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const uint32_t col = 2 * c + (e & 1);
-                                if (col < L.nc) dst[(g + 8 * (e >> 1)) * L.nc + col] += acc[e];
+                            // thread (g, c) holds the finished sums of rows g, g + 8 for column c
+                            if (c < L.nc) {
+                                dst[g * L.nc + c] += acc[0];
+                                dst[(g + 8) * L.nc + c] += acc[1];
                             }
                         }
                     }
@@ -835,7 +923,7 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
                         GemvLayout &L) {
     const uint32_t ub = ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
     L.nc = sep ? 1 : n;
-    L.ecols = sep ? 2 : 8;
+    L.ecols = sep ? 2 : 2 * n;
     const uint32_t budget = kSharedBudget;
     const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
     L.group = 8192 / per_tile;
@@ -845,7 +933,7 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
     const uint32_t tab_bytes = ty == T_IQ2_XXS ? (256 + 128) * 8 : 0;
     const uint32_t stage_cap = 46 * 1024;
     const uint32_t row_bytes = nunit * ub;
-    const uint32_t xunit = sep ? kXqUnit : kXsUnit, info_unit = sep ? 64 : 0;
+    const uint32_t xunit = kXqUnit, info_unit = sep ? 64 : 4 * 48;  // per unit: 4 quarters x float4, or 4 columns x 12 words
     // Candidate plans, best first: whole tiles, half tiles, then one copy per row of
     // ever shorter segments (1, 2, ... per row).  Contiguous rows cannot be padded:
     // when the row size is a multiple of 64 bytes the rows a warp reads together
@@ -885,7 +973,7 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
         L.rs = rs;
         L.stage_bytes = stage;
         const uint32_t per_chunk = L.ecols * cb * xunit + cb * info_unit;  // x and what goes with it
-        const uint32_t small = kBarBytes + red_bytes + kZeroBytes + tab_bytes + 64 + L.ecols * 128;
+        const uint32_t small = kBarBytes + red_bytes + tab_bytes + 64 + L.ecols * 128;
         const uint32_t min_stages = L.mode == 1 ? 4 : 2;
         if (small + min_stages * stage + per_chunk > budget) continue;
         uint32_t nstage, panel;
@@ -903,12 +991,11 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
         if (L.mode == 1) nstage &= ~1u;  // a tile takes two stages
         L.nstage = nstage;
         L.panel = panel;
-        L.es = sep ? xq_col_stride(panel * cb) : xs_col_stride(panel * cb);
+        L.es = xq_col_stride(panel * cb);
         L.xs_off = kBarBytes + nstage * stage;
         L.info_off = (L.xs_off + L.ecols * L.es + 15) & ~15u;
         L.red_off = L.info_off + panel * cb * info_unit;
-        L.zero_off = (L.red_off + red_bytes + 15) & ~15u;
-        L.tab_off = (L.zero_off + kZeroBytes + 15) & ~15u;
+        L.tab_off = (L.red_off + red_bytes + 15) & ~15u;
         L.smem_bytes = L.tab_off + tab_bytes;
         if (L.smem_bytes > budget) continue;
         // A plan that keeps all of x resident stages it once per launch; one that does
@@ -955,7 +1042,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
         case DT_BF16: return launch_t<TY, DT_BF16, true>(a, G, s, sms, dev);
         case DT_F32: return launch_t<TY, DT_F32, true>(a, G, s, sms, dev);
         }
-    } else if constexpr (TY == T_Q4_K) {
+    } else {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, false>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, false>(a, G, s, sms, dev);
@@ -981,7 +1068,7 @@ bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, 
     const uint32_t ctas = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
     const uint32_t tpc = (tiles + ctas - 1) / ctas;
     if (!gemv_layout(ty, k / 256, 1, true, tpc, a, L)) return false;
-    if (ty == T_Q4_K && n > 1 && !gemv_layout(ty, k / 256, n < 4 ? n : 4, false, tpc, a, L)) return false;
+    if (n > 1 && !gemv_layout(ty, k / 256, n < 4 ? n : 4, false, tpc, a, L)) return false;
     return true;
 }
 
@@ -991,8 +1078,8 @@ bool gemv_fast_supported(int ty, uint32_t k, uint32_t m, const void *w, const vo
     return gemv_group_supported(ty, k, 1, &m, &wp, x, xdt, n, sms);
 }
 
-// One launch covers one column (SEP) or, for Q4_K, up to four (PRE); wider
-// requests are cut into passes over consecutive columns.  `nseg` matrices of the
+// One launch covers one column (SEP) or up to four (WIDE); wider requests are cut
+// into passes over consecutive columns.  `nseg` matrices of the
 // same type and K share every launch.
 cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, const uint32_t *m, float *const *out,
                               uint32_t k, const void *x, int xdt, uint32_t n, int *status, cudaStream_t s,
@@ -1021,7 +1108,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
     const size_t xsz = xdt == DT_F32 ? 4 : 2;
     for (uint32_t c0 = 0; c0 < n;) {
         const uint32_t left = n - c0;
-        const bool sep = left == 1 || ty != T_Q4_K;
+        const bool sep = left == 1;
         const uint32_t take = sep ? 1 : (left < 4 ? left : 4);
         a.x = (const uint8_t *)x + (size_t)c0 * k * xsz;
         for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {

@@ -1,19 +1,18 @@
 // Building blocks of the decode matvec (1..8 activation columns): mbarrier /
-// bulk-copy pipeline primitives, the fp16 warp MMA of the multi-column variant.
+// bulk-copy pipeline primitives, launch arguments.
 //
 // Data path.  Weights stream from HBM into a shared-memory ring with bulk
 // asynchronous copies (cp.async.bulk, completion counted on an mbarrier) issued
 // by one producer thread, so a CTA has its whole share of a small matrix in
 // flight at once.  Consumer warps feed the blocks from shared memory to the
-// tensor cores (mma.sync m16n8k32 on bytes with s32 sums for one column, m16n8k16
-// on fp16 with fp32 sums for several); block scales are applied to the partial
-// sums in fp32.
+// integer tensor cores (mma.sync m16n8k32 on bytes, s32 sums); block scales are
+// applied to the sums afterwards.
 //
 // MMA operand layout (A = weights, 16 rows; B = activations, 8 columns): thread
 // (g = lane / 4, c = lane % 4) holds A rows g and g + 8 and B column g, both at
 // the k-slots that belong to c.  A dot product does not care which real k a slot
-// stands for as long as A and B agree, so thread c simply owns k in
-// [64c, 64c + 64) of every 256-wide unit of a row.
+// stands for as long as A and B agree, so the kernels hand every thread the k
+// that are contiguous in memory for it.
 //
 // Every wait on an mbarrier is bounded: after about a second without progress
 // the thread records a code in the status word and raises the CTA's abort flag;
@@ -131,27 +130,6 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                        uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("mul.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-__device__ __forceinline__ uint32_t h2_bcast(float v) { return pack_h2(v, v); }
-
 // Programmatic dependent launch: let the next kernel in the stream start its
 // weight prefetch while this one drains, and wait for the previous kernel's
 // results before touching activations or outputs.  Both are no-ops when the
@@ -160,21 +138,6 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// ---- fp16 activation panel of the multi-column variant ----------------------------
-// A slice of x (the columns of one pass, `nu` units of 256 k) is kept in shared
-// memory as fp16 in the order the MMA wants it: the 64 values that thread c of a
-// quad owns in unit u of panel column e start at
-//     e * es + u * kXsUnit + c * 144          (es % 128 == 64)
-// so the eight lanes that read together (two columns x four c) hit eight
-// different 16-byte bank groups.  Panel column j holds the hi halves of real
-// column j, column 4 + j the lo halves: x = hi + lo with hi = fp16(x).
-constexpr uint32_t kXsUnit = 4 * 144;
-
-__host__ __device__ inline uint32_t xs_col_stride(uint32_t cb) {
-    const uint32_t raw = cb * kXsUnit;
-    return raw + ((64u + 128u - raw % 128u) % 128u);
-}
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");

@@ -142,7 +142,8 @@ def test_narrow_gemm_vs_gemv(ctx, ty, n):
 def test_parallel_region_matches_separate_calls(ctx, ty, n):
     """Matvecs of one x inside a parallel region (the reference wraps gate || up
     and q || k || v in MetalEnc.parallel, QwenMetalEngine.swift:464-469, :691-696)
-    leave as one launch and give bit-identical results to separate calls."""
+    leave as one launch and give the results of separate calls (the units of a
+    tile may be dealt to other warps, so sums may differ in their last bits)."""
     k = SHAPES[ty][0][0]
     ms = [200, 96, 513]
     enc = CudaEnc(ctx)
@@ -157,11 +158,10 @@ def test_parallel_region_matches_separate_calls(ctx, ty, n):
     with enc.parallel():
         for t, w, o in zip(ts, ws, got):
             enc.gemm(t, X, o, w, n)
-    passes = 1 if (n == 1 or ty == GGUFType.Q4_K) else n
-    assert ctx.launches - before == passes
+    assert ctx.launches - before == 1
     torch.cuda.synchronize()
     for a, b in zip(got, want):
-        assert torch.equal(a, b)
+        assert rel_err(a.cpu().numpy(), b.cpu().numpy()) <= 1e-6
 
 
 def test_parallel_region_mixed_calls(ctx):
