@@ -877,10 +877,11 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     }
     OKF_GEMV_TRACE(8);
     if (G.nranks) {
-        // the stores above must be visible on every GPU before this CTA counts itself in
-        __threadfence_system();
+        // The stores above must be visible on every GPU before this CTA counts itself in:
+        // the barrier orders them before thread 0, whose system-wide fence then covers them.
         consumer_sync();
         if (tid == 0) {
+            __threadfence_system();
             for (uint32_t rk = 0; rk < G.nranks; rk++) atomicAdd_system(G.arrivals[rk], 1u);
             if (blockIdx.x == 0) {
                 // one CTA stays until every CTA of every rank has counted in here: when the
@@ -897,7 +898,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                         if (p.status) atomicExch(p.status, kStatusGatherTimeout);
                         break;
                     }
-                    __nanosleep(100);
+                    __nanosleep(20);
                 }
             }
         }
