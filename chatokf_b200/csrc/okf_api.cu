@@ -423,12 +423,22 @@ int okf_matmul_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff,
     if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
     const size_t xb = (size_t)n * k * sizeof(float), ob = (size_t)n * m * sizeof(float);
     if ((rc = grow(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb))) return rc;
-    if ((rc = grow(ctx, &ctx->stage_out, &ctx->stage_out_bytes, ob))) return rc;
+    // Page-locked host memory is addressable from the device: the kernel then stores the
+    // result straight into the caller's buffer and the copy back falls away.  (x is read
+    // by every CTA, so it still goes to the device first.)
+    void *dev_out = nullptr;
+    cudaPointerAttributes pa;
+    if (cudaPointerGetAttributes(&pa, out) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer &&
+        (uintptr_t)pa.devicePointer % 16 == 0)
+        dev_out = pa.devicePointer;
+    else
+        (void)cudaGetLastError();
+    if (!dev_out && (rc = grow(ctx, &ctx->stage_out, &ctx->stage_out_bytes, ob))) return rc;
     OKF_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x, xb, cudaMemcpyHostToDevice, ctx->stream));
-    rc = gemm_dispatch(ctx, type, w, woff, k, m, ctx->stage_x, DT_F32, n, ctx->stage_out, DT_F32,
+    rc = gemm_dispatch(ctx, type, w, woff, k, m, ctx->stage_x, DT_F32, n, dev_out ? dev_out : ctx->stage_out, DT_F32,
                        (okf_stream)ctx->stream, false);
     if (rc) return rc;
-    OKF_CUDA(ctx, cudaMemcpyAsync(out, ctx->stage_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!dev_out) OKF_CUDA(ctx, cudaMemcpyAsync(out, ctx->stage_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
     OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return OKF_OK;
 }

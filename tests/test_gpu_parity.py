@@ -103,6 +103,21 @@ def test_gemv_golden_fixture(ctx, ty):
     assert rel_err(got, g["matvec"]) <= GEMV_TIGHT
 
 
+def test_host_operator_with_page_locked_output(ctx):
+    """QB.matmul with the result buffer in page-locked host memory: the kernel stores
+    into it directly (no copy back); same values as with an ordinary array."""
+    ty, k, m, n = GGUFType.Q4_K, 1024, 300, 3
+    blocks = make_weights(ty, m, k, seed=8)
+    w = ctx.upload(blocks)
+    t = GGUFTensor("w", (k, m), ty)
+    X = np.stack([lcg_fill(k, 40 + c) for c in range(n)])
+    plain = QB(ctx).matmul(t, w, X, n)
+    pinned = torch.full((n, m), float("nan")).pin_memory()
+    got = QB(ctx).matmul(t, w, X, n, pinned.numpy())
+    assert np.array_equal(got, plain)
+    assert rel_err(got, oracle.matmul(ty, blocks, k, m, X, n)) <= GEMV_TIGHT
+
+
 def test_gemv_reference_selftest_shape(ctx):
     """Config 1 of the benchmark: Q8_0 2048 x 2048 with the LCG activations the
     reference's self-test uses (QwenMetalSelfTest.swift:593-609)."""
