@@ -471,7 +471,7 @@ def run_ours(args):
     enc = CudaEnc(ctx)
     stream = torch.cuda.Stream()
     wl, batch = args.workload, args.batch
-    L = Layers(ctx, wl, batch, rank, world, gather=args.gather)
+    L = Layers(ctx, wl, batch, rank, world, layers=args.layers, gather=args.gather)
     tensor_bound = batch > 8
 
     with torch.cuda.stream(stream):
@@ -595,6 +595,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="which configuration is the timed one")
     ap.add_argument("--batch", type=int, default=1, help="activation columns (tokens) per call")
+    ap.add_argument("--layers", type=int, default=None, help="layers per step (default: the workload's own count)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
                     help="N > 1 GPUs: how every rank gets the whole output (fused needs batch <= 8)")
     args = ap.parse_args()

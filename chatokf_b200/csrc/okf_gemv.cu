@@ -147,6 +147,20 @@ __device__ __forceinline__ void imma0(int (&d)[4], uint32_t a0, uint32_t a1, uin
             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
+// IQ2_XXS: byte masks (0xFF = negative) of the eight weights a 7-bit sign index stands
+// for; the eighth sign is the parity of the seven (LLM/Quantize/IQ2Grid.swift:73-85).
+// n * 0x00204081 puts bit j of a nibble on bit 8j (and on bits that the AND drops; no
+// two of its terms meet, so nothing carries); times 0xFF a set bit fills its byte.
+// Computed rather than looked up: look-ups at data-dependent addresses collide on
+// shared-memory banks, and the multiplies run on the otherwise idle FMA pipe.
+__device__ __forceinline__ uint2 iq2_sign_masks(uint32_t idx7) {
+    const uint32_t lo = idx7 & 15u, hi = (idx7 >> 4) | ((__popc(idx7) & 1u) << 3);
+    uint2 m;
+    m.x = ((lo * 0x00204081u) & 0x01010101u) * 0xFFu;
+    m.y = ((hi * 0x00204081u) & 0x01010101u) * 0xFFu;
+    return m;
+}
+
 // sum over the hi and lo bytes of x: columns 2c (hi) and 2c+1 (lo) of one row
 __device__ __forceinline__ float join_hi_lo(int hi, int lo) { return (float)(hi * 256 + lo); }
 
@@ -155,7 +169,7 @@ __device__ __forceinline__ float join_hi_lo(int hi, int lo) { return (float)(hi 
 // quarter of the unit, the byte column its MMA column stands for; zeros in the
 // lanes that feed nothing).  xi: for the two 32-wide blocks of the quarter,
 // {xs of the first, xs of the second, sum of x over the first, over the second}.
-// tab: IQ2_XXS codebook (256 x 8 magnitudes) followed by the 128 sign masks.
+// tab: IQ2_XXS codebook (256 x 8 magnitudes).
 // acc: rows g and g + 8.
 template <int TY>
 __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, uint32_t c,
@@ -258,7 +272,6 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
         lds_a2<4>(ua + 2 + 16 * c, wa);
         lds_a2<4>(ub + 2 + 16 * c, wb);
         const float da = f16bits(ld_u16(ua)), db = f16bits(ld_u16(ub));
-        const uint2 *sgn = tab + 256;
         float sum[2][2];
 #pragma unroll
         for (int sb = 0; sb < 2; sb++) {
@@ -267,7 +280,7 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
 #pragma unroll
             for (int l = 0; l < 4; l++) {
                 const uint2 ea = tab[(a0a >> (8 * l)) & 0xFF], eb = tab[(a0b >> (8 * l)) & 0xFF];
-                const uint2 ma = sgn[(a1a >> (7 * l)) & 127u], mb = sgn[(a1b >> (7 * l)) & 127u];
+                const uint2 ma = iq2_sign_masks((a1a >> (7 * l)) & 127u), mb = iq2_sign_masks((a1b >> (7 * l)) & 127u);
                 const uint32_t x0 = xf[8 * sb + 2 * l], x1 = xf[8 * sb + 2 * l + 1];
                 if (l == 0) {
                     imma0<false>(pos, ea.x, eb.x, ea.y, eb.y, x0, x1);
@@ -381,7 +394,6 @@ __device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, 
         acc[1] += xs * fb;
     } else {
         // IQ2_XXS: codebook entry c of every sub-block is this thread's eight weights
-        const uint2 *sgn = tab + 256;
         float fa = 0.f, fb = 0.f;
 #pragma unroll
         for (int b = 0; b < 8; b++) {
@@ -389,7 +401,7 @@ __device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, 
             lds_a2<2>(ua + 2 + 8 * b, wa);
             lds_a2<2>(ub + 2 + 8 * b, wb);
             const uint2 ea = tab[(wa[0] >> (8 * c)) & 0xFF], eb = tab[(wb[0] >> (8 * c)) & 0xFF];
-            const uint2 ma = sgn[(wa[1] >> (7 * c)) & 127u], mb = sgn[(wb[1] >> (7 * c)) & 127u];
+            const uint2 ma = iq2_sign_masks((wa[1] >> (7 * c)) & 127u), mb = iq2_sign_masks((wb[1] >> (7 * c)) & 127u);
             int pos[4], neg[4];
             imma0<false>(pos, ea.x, eb.x, ea.y, eb.y, xf[2 * b], xf[2 * b + 1]);
             imma0<false>(neg, ea.x & ma.x, eb.x & mb.x, ea.y & ma.y, eb.y & mb.y, xf[2 * b], xf[2 * b + 1]);
@@ -633,20 +645,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if constexpr (TY == T_IQ2_XXS) {
-        // codebook, then for every 7-bit sign index the byte mask of its negative
-        // positions: bit j of idx | parity(idx) << 7 (LLM/Quantize/IQ2Grid.swift:73-85)
+        // the codebook: 256 entries of eight magnitude bytes
         uint64_t *tw = reinterpret_cast<uint64_t *>(smem + L.tab_off);
-        for (uint32_t i = threadIdx.x; i < 256 + 128; i += kGemvThreads) {
-            if (i < 256) {
-                tw[i] = g_iq2xxs_grid[i];
-            } else {
-                const uint32_t sg = iq2_signs(i - 256);
-                uint64_t m = 0;
-                for (int j = 0; j < 8; j++)
-                    if ((sg >> j) & 1u) m |= 0xFFull << (8 * j);
-                tw[i] = m;
-            }
-        }
+        for (uint32_t i = threadIdx.x; i < 256; i += kGemvThreads) tw[i] = g_iq2xxs_grid[i];
     }
     __syncthreads();
 
@@ -931,7 +932,7 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
     if (L.group < 1) L.group = 1;
     if (L.group > tiles_per_cta) L.group = tiles_per_cta;
     const uint32_t red_bytes = L.group * per_tile;
-    const uint32_t tab_bytes = ty == T_IQ2_XXS ? (256 + 128) * 8 : 0;
+    const uint32_t tab_bytes = ty == T_IQ2_XXS ? 256 * 8 : 0;
     const uint32_t stage_cap = 46 * 1024;
     const uint32_t row_bytes = nunit * ub;
     const uint32_t xunit = kXqUnit, info_unit = sep ? 64 : 4 * 48;  // per unit: 4 quarters x float4, or 4 columns x 12 words
