@@ -321,6 +321,79 @@ def test_woff_addresses_a_tensor_inside_a_larger_buffer(ctx):
     assert rel_err(got, oracle.matvec(ty, b, k, m, x)) <= GEMV_TIGHT
 
 
+def test_fast_matvec_against_simple_kernel_on_many_shapes(ctx):
+    """Seeded sweep over types, K, M, batch width and activation type: the tensor-core
+    matvec against the warp-per-row kernel with exact decode (OKF_FLAG_SIMPLE_KERNELS)
+    on the same device buffers.  K and M are drawn so that every shared-memory plan
+    comes up: whole tiles, half tiles, row segments (aligned and not), rows that
+    alias banks, several groups of tiles per CTA, one to eight columns."""
+    rng = np.random.default_rng(2024)
+    enc = CudaEnc(ctx)
+    ks = [256, 512, 1024, 1536, 2048, 2560, 2816, 4096, 5120, 6144, 9728, 11008, 14336, 17408, 20480]
+    worst = 0.0
+    for case in range(48):
+        ty = ALL_TYPES[case % 4]
+        k = int(rng.choice(ks))
+        m = int(rng.choice([1, 7, 16, 33, 250, 777, 2048, 4999, 30000 if k <= 2048 else 1500]))
+        n = int(rng.choice([1, 1, 2, 3, 4, 5, 7, 8]))
+        tdt = [torch.float32, torch.float16, torch.bfloat16][case % 3]
+        blocks = synth.random_blocks(ty, m * k // block_elems(ty), rng)
+        w = ctx.upload(blocks)
+        t = GGUFTensor("w", (k, m), ty)
+        X = torch.from_numpy(rng.normal(size=(n, k)).astype(np.float32)).cuda().to(tdt)
+        fast = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
+        slow = torch.empty(n * m, dtype=torch.float32, device="cuda")
+        enc.gemm(t, X, fast, w, n)
+        ctx.set_flags(1)
+        try:
+            enc.gemm(t, X, slow, w, n)
+        finally:
+            ctx.set_flags(0)
+        torch.cuda.synchronize()
+        f = fast.cpu().numpy()
+        assert np.isnan(f[n * m:]).all(), (ty, k, m, n)
+        err = rel_err(f[:n * m], slow.cpu().numpy())
+        assert err <= GEMV_TIGHT, (int(ty), k, m, n, str(tdt), err)
+        worst = max(worst, err)
+    assert ctx.device_status() == 0
+
+
+def test_tensor_core_matmul_against_simple_kernel_on_many_shapes(ctx):
+    """Seeded sweep of the prefill matmul (N >= 9) against the fp32 register-tile kernel
+    with exact decode: every work plan comes up (one or two token blocks per item,
+    splits along K with the ordered reduction, token runs for left-over items),
+    all activation types, fp32 and bf16 outputs, ragged M and N."""
+    rng = np.random.default_rng(77)
+    enc = CudaEnc(ctx)
+    shapes = [(256, 19000, 300), (512, 9600, 512), (8192, 140, 64), (1024, 130, 9), (2048, 5000, 700),
+              (4096, 1000, 257), (17408, 384, 96), (320, 77, 1000), (1536, 20000, 130), (6144, 2048, 512)]
+    for case, (k, m, n) in enumerate(shapes * 2):
+        ty = ALL_TYPES[case % 4]
+        if k % block_elems(ty):
+            k = k // block_elems(ty) * block_elems(ty)
+        tdt = [torch.bfloat16, torch.float16, torch.float32][case % 3]
+        odt = torch.bfloat16 if case % 5 == 4 else torch.float32
+        blocks = synth.random_blocks(ty, m * k // block_elems(ty), rng)
+        w = ctx.upload(blocks)
+        t = GGUFTensor("w", (k, m), ty)
+        X = torch.from_numpy(rng.normal(size=(n, k)).astype(np.float32)).cuda().to(tdt)
+        fast = torch.full((n * m + 8,), float("nan"), dtype=odt, device="cuda")
+        slow = torch.empty(n * m, dtype=torch.float32, device="cuda")
+        enc.gemm(t, X, fast, w, n)
+        ctx.set_flags(1)
+        try:
+            enc.gemm(t, X, slow, w, n)
+        finally:
+            ctx.set_flags(0)
+        torch.cuda.synchronize()
+        f = fast.float().cpu().numpy()
+        assert np.isnan(f[n * m:]).all(), (int(ty), k, m, n)
+        tol = GEMM_TOL if odt == torch.float32 else GEMM_TOL + 8e-3
+        err = rel_err(f[:n * m], slow.cpu().numpy())
+        assert err <= tol, (int(ty), k, m, n, str(tdt), str(odt), err)
+    assert ctx.device_status() == 0
+
+
 def test_error_codes(ctx):
     ty, k, m = GGUFType.Q4_K, 512, 4
     w = ctx.upload(make_weights(ty, m, k, seed=1))
