@@ -550,14 +550,30 @@ __device__ __forceinline__ void stage_x_wide(uint8_t *xs, float *xw, const GemvL
                                              uint32_t u_first, uint32_t nu, uint32_t tid) {
     const uint32_t items_per_col = nu * 16;
     const uint32_t total = (L.nc * items_per_col + 31) & ~31u;
-    for (uint32_t i = tid; i < total; i += kConsumers) {
-        const bool live = i < L.nc * items_per_col;
-        const uint32_t col = live ? i / items_per_col : 0, it = live ? i % items_per_col : 0;
+    constexpr uint32_t kFlight = 3;  // items a thread has in flight: the loads go out first
+    auto where = [&](uint32_t i, bool &live, uint32_t &col, uint32_t &it) {
+        live = i < L.nc * items_per_col;
+        col = live ? i / items_per_col : 0;
+        it = live ? i % items_per_col : 0;
+    };
+    for (uint32_t base_i = tid; base_i < total; base_i += kFlight * kConsumers) {
+      XRaw<XDT> raw[kFlight];
+#pragma unroll
+      for (uint32_t r = 0; r < kFlight; r++) {
+          bool live; uint32_t col, it;
+          where(base_i + r * kConsumers, live, col, it);
+          raw[r] = load16<XDT>(x, (size_t)col * kdim + (size_t)(u_first + (it >> 4)) * 256 + (it & 15) * 16, live);
+      }
+#pragma unroll
+      for (uint32_t r = 0; r < kFlight; r++) {
+        const uint32_t i = base_i + r * kConsumers;
+        if (i >= total) break;  // the same for the whole warp
+        bool live; uint32_t col, it;
+        where(i, live, col, it);
         const uint32_t u = it >> 4, blk = (it >> 1) & 7, half = it & 1;  // unit, 32-wide block, 16-k half of it
         int q[16], qsum;
         float scale;
-        quantize16<XDT>(load16<XDT>(x, (size_t)col * kdim + (size_t)(u_first + u) * 256 + (it & 15) * 16, live), q, scale,
-                        qsum);
+        quantize16<XDT>(raw[r], q, scale, qsum);
         if (!live) continue;
         uint8_t *base = xs + (2 * col) * L.es + u * kXqUnit;
         if constexpr (TY == T_Q2_0) {
@@ -596,6 +612,7 @@ __device__ __forceinline__ void stage_x_wide(uint8_t *xs, float *xw, const GemvL
             reinterpret_cast<int *>(w12)[4 + blk] = qsum;
             if (blk == 0) w12[0] = scale;
         }
+      }
     }
 }
 
