@@ -40,7 +40,10 @@ constexpr uint32_t kBN = 256;           // tokens per accumulator (UMMA N)
 constexpr uint32_t kBK = 64;            // k per stage: 64 x 2 bytes = one 128-byte swizzle row
 constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KB
 constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KB per 256 tokens
-constexpr uint32_t kRingBytes = 4 * (kABytes + kBBytes);  // four stages of one token block, or two of two
+// Two rings.  With one token block per item: four stages of A (16 KB) and of B (32 KB).  With
+// two blocks a B stage is 64 KB: three of them and two of A, so that a B tile has two MMA
+// periods to arrive while the next A tile only has to be stored (IQ2_XXS, which also keeps its
+// codebook in shared memory, stays with two B stages).
 constexpr uint32_t kAWarps = 8;                        // warps 0..7 unpack weights (A tile)
 constexpr uint32_t kBWarps = 8;                        // warps 8..15: fp32 activations: convert the B tile;
                                                        // 16-bit activations: a second unpacking group
@@ -48,7 +51,13 @@ constexpr uint32_t kProducerWarps = kAWarps + kBWarps;
 constexpr uint32_t kTmaWarp = kProducerWarps;          // warp 16: one thread hands B tiles to the copy engine
 constexpr uint32_t kMmaWarp = kProducerWarps + 1;      // warp 17
 constexpr uint32_t kThreads = (kProducerWarps + 2 + 4) * 32;  // + four epilogue warps
-constexpr uint32_t kSmemBytes = 1024 /*align*/ + kRingBytes + 2048 /*grid*/ + 256 /*barriers*/;
+template <int TY, int NACC> struct Rings {
+    static constexpr uint32_t a_stages = NACC == 2 ? 2 : 4;
+    static constexpr uint32_t b_stages = NACC == 2 ? (TY == T_IQ2_XXS ? 2 : 3) : 4;
+    static constexpr uint32_t a_bytes = a_stages * kABytes, b_stage = NACC * kBBytes, b_bytes = b_stages * b_stage;
+    static constexpr uint32_t grid_bytes = TY == T_IQ2_XXS ? 2048 : 0;
+    static constexpr uint32_t smem = 1024 /*align*/ + a_bytes + b_bytes + grid_bytes + 256 /*barriers*/;
+};
 constexpr int kStatusGemmTimeout = 3;
 
 struct Args {
@@ -286,25 +295,29 @@ template <int TY, int XDT, typename OT, int NACC>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __grid_constant__ CUtensorMap xmap) {
     constexpr bool F16 = XDT == DT_F16;
     constexpr bool ASYNC_B = XDT != DT_F32;  // 16-bit activations come by TMA, fp32 ones are converted by eight warps
-    constexpr uint32_t kStageBytes = kABytes + NACC * kBBytes;
-    constexpr uint32_t kStages = kRingBytes / kStageBytes;  // 4 or 2
+    using R = Rings<TY, NACC>;
+    constexpr uint32_t kAStages = R::a_stages, kBStages = R::b_stages, kBStage = R::b_stage;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *stage0 = smem;
-    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + kRingBytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kRingBytes + 2048);
-    uint64_t *full = bars;                     // producers -> MMA, one per stage
-    uint64_t *empty = bars + 4;                // MMA -> producers
-    uint64_t *acc_full = bars + 8;             // MMA -> epilogue, one per accumulator
+    uint8_t *a_ring = smem, *b_ring = smem + R::a_bytes;
+    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes + R::grid_bytes);
+    uint64_t *full_a = bars, *empty_a = bars + 4;      // A producers <-> MMA, one pair per A stage
+    uint64_t *full_b = bars + 8, *empty_b = bars + 12;  // B producer(s) <-> MMA, one pair per B stage
+    uint64_t *acc_full = bars + 16;            // MMA -> epilogue, one per accumulator
     uint64_t *acc_empty = acc_full + 2;        // epilogue -> MMA
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kStages; s++) {
-            mbar_init(&full[s], kAWarps + (ASYNC_B ? 1 : kBWarps));
-            mbar_init(&empty[s], 1);
+        for (uint32_t s = 0; s < kAStages; s++) {
+            mbar_init(&full_a[s], kAWarps);
+            mbar_init(&empty_a[s], 1);
+        }
+        for (uint32_t s = 0; s < kBStages; s++) {
+            mbar_init(&full_b[s], ASYNC_B ? 1 : kBWarps);
+            mbar_init(&empty_b[s], 1);
         }
         for (uint32_t a = 0; a < 2; a++) {
             mbar_init(&acc_full[a], 1);
@@ -349,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
             if (first < kb1) cur.load(wp, first, ahalf);
             for (uint32_t kb = first; kb < kb1; kb += kGroups) {
                 const uint32_t it = it0 + (kb - kb0);
-                const uint32_t s = it % kStages, use = it / kStages;
+                const uint32_t s = it % kAStages, use = it / kAStages;
                 if (kb + kGroups < kb1) nxt.load(wp, kb + kGroups, ahalf);
                 float v[32];
                 cur.decode(v, grid);
@@ -361,13 +374,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
                     q[c4].z = arow_live ? pack16<F16>(v[8 * c4 + 4], v[8 * c4 + 5]) : 0u;
                     q[c4].w = arow_live ? pack16<F16>(v[8 * c4 + 6], v[8 * c4 + 7]) : 0u;
                 }
-                if (use > 0 && !warp_wait(&empty[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
-                uint8_t *sa = stage0 + (size_t)s * kStageBytes;
+                if (use > 0 && !warp_wait(&empty_a[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
+                uint8_t *sa = a_ring + (size_t)s * kABytes;
 #pragma unroll
                 for (int c4 = 0; c4 < 4; c4++) *reinterpret_cast<uint4 *>(sa + swz(arow, ahalf * 4 + c4)) = q[c4];
                 fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full[s]);
+                if (lane == 0) mbar_arrive(&full_a[s]);
                 cur = nxt;
             }
             it0 += kb1 - kb0;
@@ -381,18 +394,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
                 for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
                     const uint32_t nblk = wk.ntok > kBN ? NACC : 1;
                     for (uint32_t kb = wk.kb0; kb < wk.kb1; kb++, it++) {
-                        const uint32_t s = it % kStages, use = it / kStages;
-                        if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
+                        const uint32_t s = it % kBStages, use = it / kBStages;
+                        if (use > 0 && !mbar_wait(&empty_b[s], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
                             // giving up: the copies already handed over land within microseconds;
                             // stay for a while so that they do not write into a CTA that has gone
                             const long long t0 = clock64();
                             while (clock64() - t0 < 100000) {}
                             goto done;
                         }
-                        uint8_t *sb = stage0 + (size_t)s * kStageBytes + kABytes;
-                        mbar_expect_tx(&full[s], nblk * kBBytes);
+                        uint8_t *sb = b_ring + (size_t)s * kBStage;
+                        mbar_expect_tx(&full_b[s], nblk * kBBytes);
                         for (uint32_t a = 0; a < nblk; a++)
-                            tma_load_tile(sb + a * kBBytes, &xmap, kb * kBK, wk.n0 + a * kBN, &full[s]);
+                            tma_load_tile(sb + a * kBBytes, &xmap, kb * kBK, wk.n0 + a * kBN, &full_b[s]);
                     }
                 }
             }
@@ -407,9 +420,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
             for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
                 const uint32_t n0 = wk.n0;
                 for (uint32_t kb = wk.kb0; kb < wk.kb1; kb++, it++) {
-                    const uint32_t s = it % kStages, use = it / kStages;
-                    if (use > 0 && !warp_wait(&empty[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
-                    uint8_t *sb = stage0 + (size_t)s * kStageBytes + kABytes;
+                    const uint32_t s = it % kBStages, use = it / kBStages;
+                    if (use > 0 && !warp_wait(&empty_b[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
+                    uint8_t *sb = b_ring + (size_t)s * kBStage;
 #pragma unroll
                     for (uint32_t i = 0; i < kChunks; i++) {
                         const uint32_t q = t + kBWarps * 32 * i;
@@ -428,7 +441,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
                     }
                     fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&full[s]);
+                    if (lane == 0) mbar_arrive(&full_b[s]);
                 }
             }
         }
@@ -469,14 +482,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
                 tc_fence_after();
                 const uint32_t kb0 = wk.kb0, kb1 = wk.kb1;
                 for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
-                    const uint32_t s = it % kStages, use = it / kStages;
-                    if (!mbar_wait(&full[s], use & 1, abort_flag, p.status, kStatusGemmTimeout)) { ok = false; break; }
+                    const uint32_t s_a = it % kAStages, s_b = it % kBStages;
+                    if (!mbar_wait(&full_a[s_a], (it / kAStages) & 1, abort_flag, p.status, kStatusGemmTimeout) ||
+                        !mbar_wait(&full_b[s_b], (it / kBStages) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(stage0 + (size_t)s * kStageBytes);
-                    const uint64_t da = smem_desc(sa);
+                    const uint32_t sb = smem_u32(b_ring + (size_t)s_b * kBStage);
+                    const uint64_t da = smem_desc(smem_u32(a_ring + (size_t)s_a * kABytes));
 #pragma unroll
                     for (uint32_t a = 0; a < (uint32_t)NACC; a++) {
-                        const uint64_t db = smem_desc(sa + kABytes + a * kBBytes);
+                        const uint64_t db = smem_desc(sb + a * kBBytes);
                         const uint32_t d_tmem = tmem_base + (acc0 + a) * kBN;
 #pragma unroll
                         for (uint32_t k4 = 0; k4 < kBK / 16; k4++) {
@@ -484,7 +501,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
                             umma(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
                         }
                     }
-                    umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+                    umma_commit(&empty_a[s_a]);  // both stages are free once these MMAs have read them
+                    umma_commit(&empty_b[s_b]);
                 }
                 if (!ok) break;
                 for (uint32_t a = 0; a < (uint32_t)NACC; a++) umma_commit(&acc_full[acc0 + a]);
@@ -598,7 +616,7 @@ static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
     static bool attr_set[64] = {};  // the opt-in is per device
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TY, XDT, OT, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TY, XDT, OT, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Rings<TY, NACC>::smem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
@@ -610,7 +628,7 @@ static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
         cudaError_t me = encode_x_map(&xmap, a.x, a.k, a.n);
         if (me != cudaSuccess) return me;
     }
-    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, kSmemBytes, s>>>(a, xmap);
+    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, Rings<TY, NACC>::smem, s>>>(a, xmap);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || a.ksplit == 1) return e;
     const size_t count = (size_t)a.n * a.m;
