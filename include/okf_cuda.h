@@ -105,7 +105,12 @@ OKF_API int okf_gemv(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff
  * (Base/MetalEnc.swift:241-289): N == 1 runs the matvec kernel, 2 <= N <= 8
  * the narrow (speculative-verify) kernel (gemmNarrowIQ, MetalEnc.swift:222-239),
  * larger N the tensor-core tile (gemmTiled, MetalEnc.swift:377-400).  X holds
- * N*K elements of xdt; out holds N*M elements of odt (OKF_F32 or OKF_BF16). */
+ * N*K elements of xdt; out holds N*M elements of odt (OKF_F32 or OKF_BF16).
+ * Numerics: for N <= 8 (fp32 out) every 256-wide run of an activation column is
+ * reduced to 16-bit integers with one fp32 scale and the sums are exact integers
+ * (results within 1e-4 of max|y| of an fp32 evaluation on the test shapes, the
+ * same for a column at every N); the tile rounds weights and activations to
+ * 16-bit floats and accumulates in fp32 (within 1e-2). */
 OKF_API int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
              const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream);
 
@@ -114,7 +119,8 @@ OKF_API int okf_gemm(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff
  * around gate || up and q || k || v (Qwen/QwenMetalEngine.swift:464-469, :691-696).
  * Inside a region, okf_gemv / okf_gemm calls with N <= 8 that multiply the same
  * x by matrices of one type and K (up to four) are held back and leave as ONE
- * kernel launch, at okf_parallel_end or as soon as a call does not fit the set;
+ * kernel launch (one per four columns of N), at okf_parallel_end or as soon as
+ * a call does not fit the set;
  * every other call runs at once, as outside a region.  A launch error of a
  * held-back call is returned by the call that sends the set off.  Regions do
  * not nest.  Outputs of the region must not alias its inputs. */
