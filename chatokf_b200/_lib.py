@@ -47,6 +47,7 @@ SIGNATURES = {
     "okf_device_status": (_ci, [_vp, ctypes.POINTER(ctypes.c_int)]),
     "okf_set_flags": (_ci, [_vp, _u32]),
     "okf_launch_count": (_u64, [_vp]),
+    "okf_fallback_count": (_u64, [_vp]),
 }
 
 

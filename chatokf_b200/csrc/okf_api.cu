@@ -13,16 +13,11 @@ namespace {
 
 constexpr size_t kTailPad = 256;  // bytes readable past the last block of an upload
 
-
 #define OKF_CUDA(ctx, call)                                   \
     do {                                                      \
         cudaError_t e_ = (call);                              \
         if (e_ != cudaSuccess) return cuda_fail((ctx), e_);   \
     } while (0)
-
-
-
-
 
 int grow(okf_ctx *ctx, void **buf, size_t *have, size_t need) {
     if (*have >= need) return OKF_OK;
@@ -98,6 +93,7 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
             if (e != cudaSuccess) return cuda_fail(ctx, e);
             return OKF_OK;
         } else {
+            if (!simple) ctx->fallbacks++;  // a shape or alignment the tensor-core matvec does not take
             e = launch_gemv_simple(ty, wp, k, m, x, xdt, n, (float *)out, s);
         }
     } else if (!(ctx->flags & OKF_FLAG_SIMPLE_KERNELS) && gemm_tc_supported(ty, k, m, wp, x, xdt, n)) {
@@ -117,6 +113,7 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
                            ctx->sms, ctx->device);
         if (e == cudaSuccess && ksplit > 1) ctx->launches++;
     } else {
+        if (!(ctx->flags & OKF_FLAG_SIMPLE_KERNELS)) ctx->fallbacks++;
         e = launch_gemm_simple(ty, wp, k, m, x, xdt, n, out, odt, s);
     }
     if (e != cudaSuccess) return cuda_fail(ctx, e);
@@ -189,10 +186,14 @@ void okf_destroy(okf_ctx *ctx) {
 int okf_last_cuda_error(const okf_ctx *ctx) { return ctx ? ctx->last_cuda : 0; }
 okf_stream okf_ctx_stream(const okf_ctx *ctx) { return ctx ? (okf_stream)ctx->stream : nullptr; }
 uint64_t okf_launch_count(const okf_ctx *ctx) { return ctx ? ctx->launches : 0; }
+uint64_t okf_fallback_count(const okf_ctx *ctx) { return ctx ? ctx->fallbacks : 0; }
 
 int okf_sync(okf_ctx *ctx) {
     if (!ctx) return OKF_E_ARG;
     DeviceGuard g(ctx->device);
+    // matvecs a parallel region is still holding back are sent off first
+    int rc = par_flush(ctx);
+    if (rc) return rc;
     OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return OKF_OK;
 }
@@ -438,6 +439,9 @@ int okf_matmul_host(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff,
     rc = gemm_dispatch(ctx, type, w, woff, k, m, ctx->stage_x, DT_F32, n, dev_out ? dev_out : ctx->stage_out, DT_F32,
                        (okf_stream)ctx->stream, false);
     if (rc) return rc;
+    // inside a parallel region the matvec was only queued: the host twin returns a finished
+    // result, so the waiting set leaves now
+    if (ctx->par_open && (rc = par_flush(ctx))) return rc;
     if (!dev_out) OKF_CUDA(ctx, cudaMemcpyAsync(out, ctx->stage_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
     OKF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return OKF_OK;

@@ -752,7 +752,9 @@ namespace okf {
 constexpr size_t kStaticScratchFloats = (size_t)4 << 20;  // 16 MiB on every GPU that loads the library
 static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 // In host code the name above is only a stand-in for the symbol; the device address has
-// to be asked for, once per device, with that device current.
+// to be asked for, once per device, with that device current.  The cache is not
+// synchronised: two threads that meet here for the first time both look the address
+// up and both store the same value.
 static float *g_static_scratch_addr[64] = {};
 }  // namespace okf
 

@@ -478,7 +478,9 @@ __device__ __forceinline__ void quantize16(const XRaw<XDT> &raw, int (&q)[16], f
         nanprobe += __shfl_xor_sync(0xffffffffu, nanprobe, o);
     }
     const bool bad = nanprobe != nanprobe && !(amax == __int_as_float(0x7F800000));
-    const float inv = amax > 0.f ? __fdividef(kXqMax, amax) : 0.f;  // an infinite amax gives 0 and xs = inf
+    // an infinite amax gives 0 and xs = inf; a unit whose largest magnitude is below 1e-30
+    // counts as zeros (32512 / amax would overflow, and its products vanish in fp32 anyway)
+    const float inv = amax > 1e-30f ? __fdividef(kXqMax, amax) : 0.f;
     xs = bad ? __int_as_float(0x7FC00000) : amax * (1.f / kXqMax);
     int s4[4] = {0, 0, 0, 0};
 #pragma unroll
@@ -617,12 +619,6 @@ __device__ __forceinline__ void stage_x_wide(uint8_t *xs, float *xw, const GemvL
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-// Hooks for a timing harness that includes this file; they compile to nothing here.
-#ifndef OKF_GEMV_TRACE
-#define OKF_GEMV_TRACE_INIT
-#define OKF_GEMV_TRACE(tag)
-#endif
-
 // Position in the ring of stages; the producer and the consumers step through it
 // in the same order, so both keep one of these.
 struct RingPos {
@@ -650,7 +646,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     const uint32_t t1 = (uint32_t)((uint64_t)p.tiles * (blockIdx.x + 1) / gridDim.x);
     const uint32_t ntl = t1 - t0;
     const uint32_t spt = L.mode == 1 ? 2 : 1;  // stages per step (two half-tiles in mode 1)
-    OKF_GEMV_TRACE_INIT;
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
@@ -722,7 +717,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                                 bulk_g2s(dst + (size_t)r * L.rs, sg.w + (src - skew), (skew + seg + 15u) & ~15u, &full[rp.s]);
                             }
                         }
-                        OKF_GEMV_TRACE(1);
                         rp.next(L.nstage);
                     }
                 }
@@ -732,9 +726,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     }
 
     // ---- consumers
-    OKF_GEMV_TRACE(2);
     pdl_wait();  // activations come from the previous kernel; outputs may still be read by it
-    OKF_GEMV_TRACE(3);
 
     const uint32_t tid = threadIdx.x;  // 0 .. kConsumers - 1
     // A wait that gives up marks the warp dead; a dead warp skips further waits but
@@ -770,7 +762,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                 else stage_x_wide<TY, XDT>(xs, reinterpret_cast<float *>(info), L, p.x, p.k, pu0, pnu, tid);
             }
             consumer_sync();
-            OKF_GEMV_TRACE(4);
             for (uint32_t j = j0; j < j1; j++) {
                 const uint32_t u0 = j * p.cb, nu = min(p.cb, p.nunit - u0);
                 const uint32_t pu = u0 - pu0;  // first unit of the chunk inside the panel
@@ -780,7 +771,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                     const GemvSeg sg = gemv_segment(p, t0 + tl);
                     tn = min(min(L.tps, gb + gn - tl), sg.tile1 - (t0 + tl));
                     const uint32_t sA = rp.s;
-                    OKF_GEMV_TRACE(5);
                     wait_full(rp.s, rp.use);
                     rp.next(L.nstage);
                     const uint32_t sB = rp.s;
@@ -788,7 +778,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                         wait_full(rp.s, rp.use);
                         rp.next(L.nstage);
                     }
-                    OKF_GEMV_TRACE(6);
                     // rows g and g + 8 of the step's first tile
                     const uint8_t *ra = stages + (size_t)sA * L.stage_bytes + (size_t)g * L.rs;
                     const uint8_t *rb = L.mode == 1 ? stages + (size_t)sB * L.stage_bytes + (size_t)g * L.rs
@@ -867,7 +856,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                         mbar_arrive(&empty[sA]);
                         if (spt == 2) mbar_arrive(&empty[sB]);
                     }
-                    OKF_GEMV_TRACE(7);
                 }
             }
         }
@@ -893,7 +881,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         }
         if (gb + L.group < ntl) consumer_sync();  // before the buffer is zeroed again
     }
-    OKF_GEMV_TRACE(8);
     if (G.nranks) {
         // The stores above must be visible on every GPU before this CTA counts itself in:
         // the barrier orders them before thread 0, whose system-wide fence then covers them.

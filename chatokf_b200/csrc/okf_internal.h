@@ -22,6 +22,7 @@ struct okf_ctx {
     cudaStream_t stream;
     int last_cuda;
     uint64_t launches;
+    uint64_t fallbacks;  // calls that took a simple kernel because a fast one declined the shape
     // host-twin staging (device side), grown on demand
     void *stage_x;
     size_t stage_x_bytes;

@@ -84,6 +84,11 @@ class Context:
     def launches(self) -> int:
         return int(self.lib.okf_launch_count(self.h))
 
+    @property
+    def fallbacks(self) -> int:
+        """Calls that ran on the simple kernels because a fast one declined the shape."""
+        return int(self.lib.okf_fallback_count(self.h))
+
     def device_status(self) -> int:
         """0 unless a bounded wait inside a kernel gave up (okf_device_status)."""
         v = ctypes.c_int(0)

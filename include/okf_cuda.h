@@ -106,6 +106,9 @@ OKF_API int okf_gemv(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff
  * the narrow (speculative-verify) kernel (gemmNarrowIQ, MetalEnc.swift:222-239),
  * larger N the tensor-core tile (gemmTiled, MetalEnc.swift:377-400).  X holds
  * N*K elements of xdt; out holds N*M elements of odt (OKF_F32 or OKF_BF16).
+ * For deep, short matrices the tile cuts K into ranges whose partial sums live
+ * in ONE scratch buffer of the context: calls of one context that may take that
+ * route must be ordered on the GPU (same stream, or events between streams).
  * Numerics: for N <= 8 (fp32 out) every 256-wide run of an activation column is
  * reduced to 16-bit integers with one fp32 scale and the sums are exact integers
  * (results within 1e-4 of max|y| of an fp32 evaluation on the test shapes, the
@@ -170,7 +173,9 @@ OKF_API int okf_gemm_gather(okf_ctx *ctx, int type, const okf_weights *w, uint64
 OKF_API int okf_gemm_tile(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
                   const void *x, int xdt, uint32_t n, void *out, int odt, okf_stream stream);
 
-/* The same result as okf_gemm, for callers that cannot allocate device memory
+/* The matmul of okf_gemm on the tensor-core tile at every N (the same result as
+ * okf_gemm for N >= 9; for N <= 8 okf_gemm runs the narrow integer kernel, which
+ * is closer to fp32 than the tile's 16-bit operands), for callers that cannot allocate device memory
  * while they run (inside a stream capture, in a latency-bound decode loop, under
  * a host that forbids cudaMalloc after start-up).  It has no counterpart in the
  * reference.  okf_gemm's tensor-core path keeps the partial sums of its k-ranges
@@ -232,6 +237,13 @@ OKF_API int okf_set_flags(okf_ctx *ctx, uint32_t flags);
 
 /* Number of kernels this context has launched since it was created. */
 OKF_API uint64_t okf_launch_count(const okf_ctx *ctx);
+/* Number of calls that ran on the plain warp-per-row / fp32-tile kernels because
+ * the tensor-core kernels do not take the shape or alignment (K not a multiple
+ * of 256 for the matvec or of 64 for the tile, x not 16-byte aligned): correct
+ * but many times slower.  A caller that cares about speed checks that this
+ * stays 0.  Calls made under OKF_FLAG_SIMPLE_KERNELS are not counted.  No
+ * counterpart in the reference. */
+OKF_API uint64_t okf_fallback_count(const okf_ctx *ctx);
 
 #ifdef __cplusplus
 }

@@ -19,7 +19,13 @@ pytestmark = pytest.mark.gpu
 
 GEMV_TOL = 1e-3   # stated tolerance for fp32-accumulated dot products
 GEMV_TIGHT = 1e-4  # what the reference's own self-test asks of its GPU gemv (QwenMetalSelfTest.swift:580)
-GEMM_TOL = 1e-2   # bf16 operands, fp32 accumulate (the reference accepts 2e-3 for its fp16 tile)
+GEMM_TOL = 1e-2   # bf16 operands, fp32 accumulate
+GEMM_TOL_F16 = 2e-3  # fp16 operands: the bound the reference sets for its own fp16 tile (QwenMetalSelfTest.swift:443-445)
+
+
+def gemm_tol(xdt, odt=F32):
+    """Bound for the tensor-core matmul: by operand type, plus bf16 rounding of a bf16 result."""
+    return (GEMM_TOL_F16 if xdt in (F16, torch.float16) else GEMM_TOL) + (8e-3 if odt in (BF16, torch.bfloat16) else 0.0)
 
 TORCH_DT = {F32: torch.float32, F16: torch.float16, BF16: torch.bfloat16}
 
@@ -219,8 +225,7 @@ def test_gemm_vs_oracle(ctx, ty, xdt, odt):
         torch.cuda.synchronize()
         o = out.float().cpu().numpy()
         assert np.isnan(o[n * m:]).all()
-        tol = GEMM_TOL if odt == F32 else GEMM_TOL + 8e-3  # + bf16 rounding of the result
-        assert rel_err(o[:n * m].reshape(n, m), ref) <= tol, (ty, k, m, n)
+        assert rel_err(o[:n * m].reshape(n, m), ref) <= gemm_tol(xdt, odt), (ty, k, m, n)
 
 
 @pytest.mark.parametrize("m,n", [(6400, 768), (10240, 512), (9728, 500)])
@@ -388,7 +393,7 @@ def test_tensor_core_matmul_against_simple_kernel_on_many_shapes(ctx):
         torch.cuda.synchronize()
         f = fast.float().cpu().numpy()
         assert np.isnan(f[n * m:]).all(), (int(ty), k, m, n)
-        tol = GEMM_TOL if odt == torch.float32 else GEMM_TOL + 8e-3
+        tol = gemm_tol(tdt, odt)
         err = rel_err(f[:n * m], slow.cpu().numpy())
         assert err <= tol, (int(ty), k, m, n, str(tdt), str(odt), err)
     assert ctx.device_status() == 0
@@ -450,3 +455,147 @@ def test_staged_faults_are_seeded_and_host_side(ctx):
     assert 0 < sum(p1) < 40 and l1 == 40 - sum(p1)
     enc.gemv(t, x, out, w)
     torch.cuda.synchronize()
+
+
+# ---- activations that stress the 16-bit reduction of x ---------------------------
+
+def _pattern_units(kind, k, rng):
+    """One activation column whose 256-wide units follow an awkward pattern."""
+    nu = k // 256
+    x = rng.normal(size=(nu, 256)).astype(np.float32)
+    if kind == "outlier_1e2":
+        x[np.arange(nu), rng.integers(0, 256, nu)] *= np.float32(1e2)
+    elif kind == "outlier_1e4":
+        x[np.arange(nu), rng.integers(0, 256, nu)] = np.float32(1e4) * np.sign(rng.normal(size=nu)).astype(np.float32)
+    elif kind == "one_hot":
+        hot = rng.integers(0, 256, nu)
+        x[:] = 0
+        x[np.arange(nu), hot] = rng.normal(size=nu).astype(np.float32) + 3
+    elif kind == "all_equal":
+        x[:] = np.float32(0.7311)
+    elif kind == "alternating_max":
+        x[:] = np.float32(60000.0) * np.where(np.arange(256) % 2, -1, 1).astype(np.float32)
+    elif kind == "f16_subnormal":
+        x[:] = (rng.integers(1, 1024, size=(nu, 256)) * 2.0 ** -24).astype(np.float32) * np.sign(x)
+    elif kind == "below_bit_16":
+        x[:] = np.float32(1.0) + rng.integers(0, 128, size=(nu, 256)).astype(np.float32) * np.float32(2.0 ** -23)
+    elif kind == "zero_unit_between_large":
+        x *= np.float32(1e3)
+        x[1::2] = 0
+    elif kind == "f32_subnormal_unit":
+        x[0] = np.float32(1e-41) * np.sign(x[0])
+    elif kind == "mixed_scales":
+        x *= (10.0 ** rng.integers(-6, 6, size=(nu, 1))).astype(np.float32)
+    else:
+        raise ValueError(kind)
+    return x.reshape(-1)
+
+
+PATTERNS = ["outlier_1e2", "outlier_1e4", "one_hot", "all_equal", "alternating_max", "f16_subnormal",
+            "below_bit_16", "zero_unit_between_large", "f32_subnormal_unit", "mixed_scales"]
+
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("n", [1, 4])
+def test_awkward_activations_stay_within_the_stated_tolerance(ctx, ty, n):
+    """The decode kernels reduce every 256-wide unit of a column of x to 16-bit integers
+    with one scale.  Real residual streams are not N(0, 1): they carry outlier channels,
+    one-hot and constant stretches, values near the bottom of the fp16 range.  Every such
+    pattern, as fp32 / fp16 / bf16 input, must stay within the stated 1e-3 of max|y|
+    against the fp32 oracle (the reference's metric, QwenMetalSelfTest.swift:575-580); the
+    distance to a float64 evaluation is reported beside it."""
+    k, m = 2048, 96
+    blocks = make_weights(ty, m, k, seed=31)
+    w = ctx.upload(blocks)
+    t = GGUFTensor("w", (k, m), ty)
+    enc = CudaEnc(ctx)
+    rng = np.random.default_rng(1234 + int(ty) + n)
+    worst, worst64 = {}, {}
+    for kind in PATTERNS:
+        for xdt in (F32, F16, BF16):
+            if kind == "below_bit_16" and xdt != F32:
+                continue  # 16-bit floats cannot hold the pattern
+            if kind == "f32_subnormal_unit" and xdt == F16:
+                continue
+            X = np.stack([_pattern_units(kind, k, rng) for _ in range(n)])
+            Xd = dev(X, TORCH_DT[xdt])
+            Xr = Xd.float().cpu().numpy()
+            ref = oracle.matmul(ty, blocks, k, m, Xr, n)
+            ref64 = oracle.matmul_f64(ty, blocks, k, m, Xr, n)
+            out = torch.full((n, m), float("nan"), dtype=torch.float32, device="cuda")
+            enc.gemm(t, Xd, out, w, n)
+            torch.cuda.synchronize()
+            o = out.cpu().numpy()
+            assert np.isfinite(o).all(), (kind, xdt)
+            e, e64 = rel_err(o, ref), rel_err(o, ref64)
+            worst[kind] = max(worst.get(kind, 0.0), e)
+            worst64[kind] = max(worst64.get(kind, 0.0), e64)
+            assert e <= GEMV_TOL, (GGUFType(ty).name, n, kind, xdt, e)
+    print(f"\n{GGUFType(ty).name} n={n}: worst vs fp32 oracle / vs float64: " +
+          ", ".join(f"{kd} {worst[kd]:.1e}/{worst64[kd]:.1e}" for kd in PATTERNS))
+    assert ctx.device_status() == 0
+
+
+# ---- the on-device yardstick itself, and the full-size prefill shapes, against the oracle ----
+
+@pytest.mark.parametrize("ty", ALL_TYPES)
+def test_simple_kernels_vs_oracle(ctx, ty):
+    """The warp-per-row matvec and the fp32 register-tile matmul (OKF_FLAG_SIMPLE_KERNELS)
+    are what the seeded sweeps compare the fast kernels with; here they meet the oracle
+    themselves.  They decode exactly and accumulate in fp32, so the matvec bound applies."""
+    enc = CudaEnc(ctx)
+    ctx.set_flags(1)
+    try:
+        for k, m, n in [(1024, 131, 1), (1024, 131, 5), (1024, 131, 77), (2048, 200, 33)]:
+            blocks = make_weights(ty, m, k, seed=k + n)
+            X = np.stack([lcg_fill(k, 300 + c) for c in range(n)])
+            before = ctx.launches
+            out = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
+            enc.gemm(GGUFTensor("w", (k, m), ty), dev(X), out, ctx.upload(blocks), n)
+            torch.cuda.synchronize()
+            assert ctx.launches == before + 1
+            o = out.cpu().numpy()
+            assert np.isnan(o[n * m:]).all()
+            assert rel_err(o[:n * m].reshape(n, m), oracle.matmul(ty, blocks, k, m, X, n)) <= GEMV_TIGHT, (k, m, n)
+    finally:
+        ctx.set_flags(0)
+
+
+@pytest.mark.parametrize("k,m", [(5120, 17408), (17408, 5120)])
+def test_prefill_config_full_size_sampled_rows_vs_oracle(ctx, k, m):
+    """The 512-token Q4_K prefill shapes at full size, bf16 activations: 32 rows picked
+    across M, all 512 tokens, against the oracle run on those rows."""
+    ty, n = GGUFType.Q4_K, 512
+    rng = np.random.default_rng(k)
+    pool = synth.quantize(ty, rng.normal(0, 0.02, size=4096 * 256).astype(np.float32)).reshape(4096, -1)
+    blocks = pool[rng.integers(0, 4096, size=m * k // 256)].reshape(-1)
+    X = rng.normal(size=(n, k)).astype(np.float32)
+    Xd = dev(X, torch.bfloat16)
+    out = torch.full((n * m + 8,), float("nan"), dtype=torch.float32, device="cuda")
+    CudaEnc(ctx).gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
+    torch.cuda.synchronize()
+    o = out.cpu().numpy()
+    assert np.isnan(o[n * m:]).all()
+    o = o[:n * m].reshape(n, m)
+    rows = np.unique(np.concatenate([[0, 127, 128, m - 1], rng.integers(0, m, size=28)]))
+    rb = row_byte_count(ty, k)
+    ref = oracle.matmul(ty, blocks.reshape(m, rb)[rows].reshape(-1), k, rows.size, Xd.float().cpu().numpy(), n)
+    assert rel_err(o[:, rows], ref) <= GEMM_TOL
+    assert ctx.device_status() == 0
+
+
+def test_host_twin_inside_a_parallel_region_returns_a_finished_result(ctx):
+    """QB.matvec between okf_parallel_begin and okf_parallel_end: the narrow matvec is
+    held back by the region, but the host twin promises the result on return, so it
+    sends the waiting set off itself."""
+    ty, k, m = GGUFType.Q4_K, 1024, 64
+    blocks = make_weights(ty, m, k, seed=12)
+    w = ctx.upload(blocks)
+    t = GGUFTensor("w", (k, m), ty)
+    x = lcg_fill(k, 3)
+    enc = CudaEnc(ctx)
+    with enc.parallel():
+        got = QB(ctx).matvec(t, w, x, np.full(m, np.nan, dtype=np.float32))
+        assert np.isfinite(got).all()
+    assert rel_err(got, oracle.matvec(ty, blocks, k, m, x)) <= GEMV_TIGHT
+    assert ctx.fallbacks == 0

@@ -1,4 +1,5 @@
 """The IQ2_XXS codebook header against its sources (CPU only)."""
+import os
 import re
 from pathlib import Path
 
@@ -7,7 +8,8 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 HEADER = ROOT / "chatokf_b200" / "csrc" / "iq2xxs_tables.h"
-REF = Path("/root/reference/LLM/Quantize/IQ2Grid.swift")
+# where a checkout of the reference lives, if there is one on this machine
+REF = Path(os.environ.get("CHATOKF_REFERENCE", "/root/reference")) / "LLM" / "Quantize" / "IQ2Grid.swift"
 
 
 def header_tables():

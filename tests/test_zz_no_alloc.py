@@ -14,6 +14,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from chatokf_b200.enc import CudaEnc, GGUFTensor, OkfError
 from chatokf_b200.gguf_types import GGUFType
 from helpers import lcg_fill, make_weights, rel_err
@@ -23,6 +24,7 @@ pytestmark = pytest.mark.gpu
 # the two entry points may cut K into a different number of ranges, so their fp32
 # sums differ in rounding only; 1e-5 is the bound the narrow-vs-matvec test uses
 SAME_TOL = 1e-5
+ORACLE_TOL = 1e-2  # the tensor-core matmul's bound with bf16 operands (tests/test_gpu_parity.py)
 
 
 def test_noalloc_matches_gemm_twice_in_a_row(ctx):
@@ -43,6 +45,9 @@ def test_noalloc_matches_gemm_twice_in_a_row(ctx):
             g = got.cpu().numpy()
             assert np.isnan(g[n * m:]).all(), "wrote past the N * M outputs"
             assert rel_err(g[:n * m].reshape(n, m), want.cpu().numpy()) <= SAME_TOL, (ty, call)
+            # and, since both run the same tile kernel, against the CPU oracle as well
+            ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
+            assert rel_err(g[:n * m].reshape(n, m), ref) <= ORACLE_TOL, (ty, call)
     assert ctx.device_status() == 0
 
 
