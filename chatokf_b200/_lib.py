@@ -70,6 +70,7 @@ SIGNATURES.update({
     "okf_shared_free": (_ci, [_vp, _vp]),
     "okf_copy_to_host": (_ci, [_vp, _vp, _vp, _sz]),
     "okf_gemm_gather": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _ci, _u32, ctypes.POINTER(Gather), _vp]),
+    "okf_gather_wait": (_ci, [_vp, _vp]),
 })
 
 _lib = None

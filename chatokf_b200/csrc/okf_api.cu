@@ -34,6 +34,15 @@ int grow(okf_ctx *ctx, void **buf, size_t *have, size_t need) {
     return OKF_OK;
 }
 
+// A gathered launch waits for the exchange launched before it and becomes the one the
+// next launch waits for.
+void gather_chain(okf_ctx *ctx, GemvGatherPlan &plan) {
+    plan.wait_arrivals = ctx->last_arrivals;
+    plan.wait_epoch = ctx->last_epoch;
+    ctx->last_arrivals = plan.arrivals[plan.rank];
+    ctx->last_epoch = plan.epoch;
+}
+
 // Launch what a parallel region has collected.
 int par_flush(okf_ctx *ctx) {
     const uint32_t cnt = ctx->par_count;
@@ -44,14 +53,18 @@ int par_flush(okf_ctx *ctx) {
     cudaError_t e = cudaSuccess;
     if (cnt > 1 && gemv_group_supported(ctx->par_type, ctx->par_k, cnt, ctx->par_m, ctx->par_w, ctx->par_x,
                                         ctx->par_xdt, ctx->par_n, ctx->sms)) {
+        if (ctx->par_gathers) gather_chain(ctx, ctx->par_gather);
         e = launch_gemv_group(ctx->par_type, cnt, ctx->par_w, ctx->par_m, ctx->par_out, ctx->par_k, ctx->par_x,
                               ctx->par_xdt, ctx->par_n, ctx->dev_status, ctx->par_stream, ctx->sms, ctx->device,
                               &ctx->launches, ctx->par_gathers ? &ctx->par_gather : nullptr);
     } else {
-        // one launch per matrix; with a gather each one is an exchange of its own on the set's counter
+        // One launch per matrix; with a gather each one is an exchange of its own on the set's
+        // counter.  The count an exchange is complete at is a running total that every launch
+        // adds its own CTAs to, so exchanges of different grid sizes may share a counter.
         for (uint32_t i = 0; i < cnt && e == cudaSuccess; i++) {
             GemvGatherPlan one = ctx->par_gather;
             one.seg[0] = ctx->par_gather.seg[i];
+            if (ctx->par_gathers) gather_chain(ctx, one);
             e = launch_gemv_group(ctx->par_type, 1, &ctx->par_w[i], &ctx->par_m[i], &ctx->par_out[i], ctx->par_k,
                                   ctx->par_x, ctx->par_xdt, ctx->par_n, ctx->dev_status, ctx->par_stream, ctx->sms,
                                   ctx->device, &ctx->launches, ctx->par_gathers ? &one : nullptr);
@@ -383,9 +396,24 @@ int okf_gemm_gather(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff,
     DeviceGuard g(ctx->device);
     if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
     float *none = nullptr;
+    gather_chain(ctx, plan);
     cudaError_t e = launch_gemv_group(type, 1, &wp, &m, &none, k, x, xdt, n, ctx->dev_status, s, ctx->sms,
                                       ctx->device, &ctx->launches, &plan);
     return e == cudaSuccess ? OKF_OK : cuda_fail(ctx, e);
+}
+
+int okf_gather_wait(okf_ctx *ctx, okf_stream stream) {
+    if (!ctx) return OKF_E_ARG;
+    int rc = par_flush(ctx);
+    if (rc) return rc;
+    if (!ctx->last_arrivals) return OKF_OK;
+    DeviceGuard g(ctx->device);
+    if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+    cudaError_t e = launch_gather_wait(ctx->last_arrivals, ctx->last_epoch, ctx->dev_status, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e);
+    ctx->last_arrivals = ctx->last_epoch = nullptr;
+    ctx->launches++;
+    return OKF_OK;
 }
 
 int okf_gemm_tile(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,

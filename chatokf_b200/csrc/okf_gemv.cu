@@ -55,10 +55,12 @@ struct GemvLayout {
     uint32_t es;           // bytes between columns of the x panel
     uint32_t panel;        // k-chunks whose slice of x is staged together
     uint32_t xs_off, info_off, red_off, tab_off;  // byte offsets in dynamic shared memory
+    uint32_t tab_copies;   // IQ2_XXS: copies of every codebook entry, side by side (a power of two)
     uint32_t smem_bytes;
 };
 
-constexpr uint32_t kBarBytes = 256;
+constexpr uint32_t kBarBytes = 384;   // barriers and the abort flag, then 128 bytes of zeros at kZeroOff
+constexpr uint32_t kZeroOff = 256;    // what the lanes that feed nothing into an MMA read instead of x
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kConsumers = kGemvWarps * 32;
 // SEP x panel: a unit of a byte column is its 256 bytes in k order, except that
@@ -77,6 +79,55 @@ __host__ __device__ inline uint32_t xq_piece_offset(uint32_t c, uint32_t piece) 
 }
 
 __device__ __forceinline__ uint4 lds128(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
+
+// Shared-memory loads by 32-bit shared-window address: the one-column path does
+// all its address arithmetic in 32 bits.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+// 4 * NW bytes from a 2-byte aligned shared address: aligned words and a funnel shift
+template <int NW>
+__device__ __forceinline__ void lds_a2(uint32_t a, uint32_t (&out)[NW]) {
+    const uint32_t base = a & ~3u, sh = (a & 2u) * 8u;
+    uint32_t w[NW + 1];
+#pragma unroll
+    for (int i = 0; i <= NW; i++) w[i] = lds32(base + 4 * i);
+#pragma unroll
+    for (int i = 0; i < NW; i++) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
+}
+__device__ __forceinline__ uint2 lds64(const uint8_t *p) { return *reinterpret_cast<const uint2 *>(p); }
+__device__ __forceinline__ int ubyte(uint32_t v, int i) { return (int)__byte_perm(v, 0, 0x4440 + i); }
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t x) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(x) : "memory");
+}
+__device__ __forceinline__ void sts16(uint32_t a, uint32_t x) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "r"(x) : "memory");
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t v;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(a), "r"(b), "r"(sel));
+    return v;
+}
 
 // 4 * NW bytes from a 2-byte aligned shared-memory address, as aligned 32-bit
 // loads plus a funnel shift when the address is 2 mod 4.
@@ -165,23 +216,63 @@ __device__ __forceinline__ uint2 iq2_sign_masks(uint32_t idx7) {
 __device__ __forceinline__ float join_hi_lo(int hi, int lo) { return (float)(hi * 256 + lo); }
 
 // ---- per-unit arithmetic, SEP -------------------------------------------------
-// ua / ub: the unit in rows g and g + 8.  xf: this thread's 64 bytes of x (its
-// quarter of the unit, the byte column its MMA column stands for; zeros in the
-// lanes that feed nothing).  xi: for the two 32-wide blocks of the quarter,
-// {xs of the first, xs of the second, sum of x over the first, over the second}.
-// tab: IQ2_XXS codebook (256 x 8 magnitudes).
-// acc: rows g and g + 8.
+// What a thread works out once per launch for the one-column path.
+struct SepConst {
+    uint32_t qoff;          // where this thread's share of a unit starts (bytes from the unit's start)
+    uint32_t hoff;          // Q2_0: where the block that share lies in starts
+    uint32_t sel, m1, m2;   // Q4_K: how to pick this thread's 6-bit scales and mins out of the 12 bytes
+    bool low;               // Q4_K: sub-blocks 0..3 (plain 6-bit fields) or 4..7 (split fields)
+    uint32_t tab_lane;      // IQ2_XXS: shared address of this lane's copy of codebook entry 0
+    uint32_t tab_stride;    // IQ2_XXS: bytes between codebook entries (copies of one entry lie side by side)
+};
 template <int TY>
-__device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, uint32_t c,
-                                         const uint32_t (&xf)[16], const float4 &xi, const uint2 *tab,
-                                         float (&acc)[2]) {
+__device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_t tab, uint32_t tab_copies) {
+    SepConst k = {};
+    if constexpr (TY == T_Q4_K) {
+        k.qoff = 16 + 32 * c;
+        k.sel = (c & 1) ? 0x7632u : 0x5410u;
+        k.low = c < 2;
+        k.m1 = k.low ? 0x3F3F3F3Fu : 0x0F0F0F0Fu;
+        k.m2 = k.low ? 0u : 0x30303030u;
+    } else if constexpr (TY == T_Q8_0) {
+        k.qoff = 68 * c;
+    } else if constexpr (TY == T_Q2_0) {
+        k.hoff = 34 * (c >> 1);
+        k.qoff = k.hoff + 2 + 16 * (c & 1);
+    } else {
+        k.qoff = 2 + 16 * c;
+        k.tab_lane = tab + (lane & (tab_copies - 1)) * 8;
+        k.tab_stride = tab_copies * 8;
+    }
+    return k;
+}
+
+// IQ2_XXS: byte masks (0xFF = negative) of the eight weights a 7-bit sign index stands
+// for; the eighth sign is the parity of the seven (LLM/Quantize/IQ2Grid.swift:73-85).
+// One multiply puts sign bit j on the top bit of byte j (the shifted copies of a 7-bit
+// number do not overlap, so nothing carries), and a byte permute in its
+// sign-replicating mode fills each byte with its top bit.
+__device__ __forceinline__ void iq2_sign_bytes(uint32_t idx7, uint32_t &lo, uint32_t &hi) {
+    const uint32_t par = (uint32_t)__popc(idx7) << 31;
+    lo = prmt(idx7 * 0x10204080u, 0u, 0xBA98u);        // signs 0..3: shifts 7, 14, 21, 28
+    hi = prmt(idx7 * 0x00020408u + par, 0u, 0xBA98u);  // signs 4..6: shifts 3, 10, 17; parity on bit 31
+}
+
+// ua / ub: shared addresses of the unit in rows g and g + 8.  xf: this thread's 64
+// bytes of x (its quarter of the unit, the byte column its MMA column stands for; zeros
+// in the lanes that feed nothing).  xi: {scale of x in this unit, integer sum of x over
+// the first 32-wide block of the quarter, over the second, -}.  acc: rows g and g + 8.
+template <int TY>
+__device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepConst &K, const uint32_t (&xf)[16],
+                                         const uint4 &xi, float (&acc)[2]) {
+    const float xs = __uint_as_float(xi.x);
     if constexpr (TY == T_Q4_K) {
         // {f16 d; f16 dmin; u8 scales[12]; u8 qs[128]} (LLM/Quantize/KQuants.swift:104-125).
         // Group c of qs (32 bytes): low nibbles = sub-block 2c, high = 2c+1, both in k order.
-        // The high nibbles stay where they are (16 x the value); 1/16 goes into the scale.
+        // The high nibbles stay where they are (16 x the value); the sums are shifted back.
         const uint4 ha = lds128(ua), hb = lds128(ub);
-        const uint4 a0 = lds128(ua + 16 + 32 * c), a1 = lds128(ua + 32 + 32 * c);
-        const uint4 b0 = lds128(ub + 16 + 32 * c), b1 = lds128(ub + 32 + 32 * c);
+        const uint4 a0 = lds128(ua + K.qoff), a1 = lds128(ua + K.qoff + 16);
+        const uint4 b0 = lds128(ub + K.qoff), b1 = lds128(ub + K.qoff + 16);
         const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
         const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         const uint32_t ml = 0x0F0F0F0Fu, mh = 0xF0F0F0F0u;
@@ -194,21 +285,33 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
             imma<false>(hi, wa[2 * i] & mh, wb[2 * i] & mh, wa[2 * i + 1] & mh, wb[2 * i + 1] & mh, xf[8 + 2 * i],
                         xf[9 + 2 * i]);
         }
-        uint32_t sc, mn;
-        q4k_scale_min2(ha, hb, c, sc, mn);
-        const float da = f16bits(ha.x & 0xFFFF), dma = f16bits(ha.x >> 16);
-        const float db = f16bits(hb.x & 0xFFFF), dmb = f16bits(hb.x >> 16);
-        const float x0 = xi.x, x1 = xi.y * 0.0625f;
-        acc[0] += da * (byte_to_f32(sc, 0) * (x0 * join_hi_lo(lo[0], lo[1])) + byte_to_f32(sc, 1) * (x1 * join_hi_lo(hi[0], hi[1]))) -
-                  dma * (byte_to_f32(mn, 0) * xi.z + byte_to_f32(mn, 1) * xi.w);
-        acc[1] += db * (byte_to_f32(sc, 2) * (x0 * join_hi_lo(lo[2], lo[3])) + byte_to_f32(sc, 3) * (x1 * join_hi_lo(hi[2], hi[3]))) -
-                  dmb * (byte_to_f32(mn, 2) * xi.z + byte_to_f32(mn, 3) * xi.w);
+        // 6-bit (scale, min) of sub-blocks 2c and 2c+1 of both rows (ggml get_scale_min_k4,
+        // LLM/Quantize/KQuants.swift:86-101) as bytes {row a: 2c, 2c+1, row b: 2c, 2c+1},
+        // without a branch: the two cases differ in where the low bits come from.
+        const uint32_t pa = prmt(ha.y, hb.y, K.sel), pb = prmt(ha.z, hb.z, K.sel), pe = prmt(ha.w, hb.w, K.sel);
+        const uint32_t sc = ((K.low ? pa : pe) & K.m1) | ((pa >> 2) & K.m2);
+        const uint32_t mn = ((K.low ? pb : (pe >> 4)) & K.m1) | ((pb >> 2) & K.m2);
+        // Integer all the way: |sum of 32 nibbles x 16-bit x| < 2^24, times a 6-bit scale
+        // < 2^30, two of them < 2^31.
+        const int jla = lo[0] * 256 + lo[1], jha = (hi[0] * 256 + hi[1]) >> 4;
+        const int jlb = lo[2] * 256 + lo[3], jhb = (hi[2] * 256 + hi[3]) >> 4;
+        const int sa = ubyte(sc, 0) * jla + ubyte(sc, 1) * jha, sb = ubyte(sc, 2) * jlb + ubyte(sc, 3) * jhb;
+        const int x0 = (int)xi.y, x1 = (int)xi.z;
+        const int ma = ubyte(mn, 0) * x0 + ubyte(mn, 1) * x1, mb = ubyte(mn, 2) * x0 + ubyte(mn, 3) * x1;
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&ha.x));
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&hb.x));
+        acc[0] += xs * (fa.x * (float)sa - fa.y * (float)ma);
+        acc[1] += xs * (fb.x * (float)sb - fb.y * (float)mb);
     } else if constexpr (TY == T_Q8_0) {
         // eight blocks {f16 d; i8 q[32]} (LLM/Gemma/Gemma4Quant.swift:51-69); thread c
-        // takes blocks 2c and 2c+1; the quants go into the MMA as they are.
+        // takes blocks 2c and 2c+1: {d0, q0[32], d1, q1[32]} = 17 words (units start on
+        // 16-byte boundaries, 68c is a multiple of 4); the quants go into the MMA as they are.
         uint32_t wa[17], wb[17];
-        lds_a2<17>(ua + 68 * c, wa);  // {d0, q0[32], d1, q1[32]} = 68 bytes, 2-byte aligned
-        lds_a2<17>(ub + 68 * c, wb);
+#pragma unroll
+        for (int i = 0; i < 17; i++) {
+            wa[i] = lds32(ua + K.qoff + 4 * i);
+            wb[i] = lds32(ub + K.qoff + 4 * i);
+        }
         // word 0 = d0 | q0[0..1] << 16 ...: shift the first run of quants by two bytes;
         // the second run (after d1 in the high half of word 8) starts on word 9
         uint32_t qa[16], qb[16];
@@ -229,23 +332,21 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
         }
         const float da0 = f16bits(wa[0] & 0xFFFF), da1 = f16bits(wa[8] >> 16);
         const float db0 = f16bits(wb[0] & 0xFFFF), db1 = f16bits(wb[8] >> 16);
-        acc[0] += da0 * (xi.x * join_hi_lo(lo[0], lo[1])) + da1 * (xi.y * join_hi_lo(hi[0], hi[1]));
-        acc[1] += db0 * (xi.x * join_hi_lo(lo[2], lo[3])) + db1 * (xi.y * join_hi_lo(hi[2], hi[3]));
+        acc[0] += xs * (da0 * join_hi_lo(lo[0], lo[1]) + da1 * join_hi_lo(hi[0], hi[1]));
+        acc[1] += xs * (db0 * join_hi_lo(lo[2], lo[3]) + db1 * join_hi_lo(hi[2], hi[3]));
     } else if constexpr (TY == T_Q2_0) {
         // two blocks {f16 d; u8 qs[32]} of 128 ternary codes, weight = (code - 1) * d
         // (LLM/Base/Quant.swift:2-25).  Thread c takes half (c & 1) of block c >> 1:
         // 16 bytes = 64 codes; byte t holds k 4t .. 4t+3.  Masking code s of every
         // byte of a word in place gives 4^s times the codes of k = s, 4+s, 8+s, 12+s
         // (x is staged in that order); the factors are undone on the integer sums.
-        const uint8_t *pa = ua + 34 * (c >> 1), *pb = ub + 34 * (c >> 1);
         uint32_t wa[4], wb[4];
-        lds_a2<4>(pa + 2 + 16 * (c & 1), wa);
-        lds_a2<4>(pb + 2 + 16 * (c & 1), wb);
-        const float da = f16bits(ld_u16(pa)), db = f16bits(ld_u16(pb));
-        float sum[2][2];  // [32-wide half][row], times 64
+        lds_a2<4>(ua + K.qoff, wa);
+        lds_a2<4>(ub + K.qoff, wb);
+        const float da = f16bits(lds16(ua + K.hoff)), db = f16bits(lds16(ub + K.hoff));
+        int t[4] = {0, 0, 0, 0};  // both 32-wide halves together, times 64
 #pragma unroll
         for (int sub = 0; sub < 2; sub++) {
-            int t[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int s = 0; s < 4; s++) {
                 const uint32_t m = 0x03030303u << (2 * s);
@@ -255,48 +356,50 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
 #pragma unroll
                 for (int e = 0; e < 4; e++) t[e] = t[e] + d[e] * (64 >> (2 * s));
             }
-            sum[sub][0] = join_hi_lo(t[0], t[1]);
-            sum[sub][1] = join_hi_lo(t[2], t[3]);
         }
-        const float s = 0.015625f;
-        acc[0] += da * (s * (xi.x * sum[0][0] + xi.y * sum[1][0]) - xi.z - xi.w);
-        acc[1] += db * (s * (xi.x * sum[0][1] + xi.y * sum[1][1]) - xi.z - xi.w);
+        const float xsum = (float)((int)xi.y + (int)xi.z);
+        acc[0] += xs * da * (0.015625f * join_hi_lo(t[0], t[1]) - xsum);
+        acc[1] += xs * db * (0.015625f * join_hi_lo(t[2], t[3]) - xsum);
     } else {
         // IQ2_XXS {f16 d; 8 x (u32 a0: four codebook indices, u32 a1: four 7-bit sign
         // indices + 4-bit scale)} (LLM/Quantize/IQ2XXS.swift:34-53).  Thread c takes
         // sub-blocks 2c and 2c+1.  A codebook entry is eight magnitude bytes = the two
-        // A registers of one row; sum(sign * mag * x) = sum(mag * x) - 2 * sum over the
-        // negative positions, the second from the magnitudes ANDed with the sign's byte
-        // mask.  db = d * (0.5 + s) * 0.25 is applied in fp32.
+        // A registers of one row.  Signs: XOR with the sign's byte mask turns a magnitude
+        // m into the signed byte -(m + 1); a second MMA on the masks themselves (255 per
+        // negative weight) gives 255 x the sum of x over the negative weights, which puts
+        // the missing 1 back: sum(sign * m * x) = D1 + D2 / 255.
         uint32_t wa[4], wb[4];
-        lds_a2<4>(ua + 2 + 16 * c, wa);
-        lds_a2<4>(ub + 2 + 16 * c, wb);
-        const float da = f16bits(ld_u16(ua)), db = f16bits(ld_u16(ub));
+        lds_a2<4>(ua + K.qoff, wa);
+        lds_a2<4>(ub + K.qoff, wb);
+        const float da = f16bits(lds16(ua)), db = f16bits(lds16(ub));
         float sum[2][2];
 #pragma unroll
         for (int sb = 0; sb < 2; sb++) {
             const uint32_t a0a = wa[2 * sb], a1a = wa[2 * sb + 1], a0b = wb[2 * sb], a1b = wb[2 * sb + 1];
-            int pos[4], neg[4];
+            int d1[4], d2[4];
 #pragma unroll
             for (int l = 0; l < 4; l++) {
-                const uint2 ea = tab[(a0a >> (8 * l)) & 0xFF], eb = tab[(a0b >> (8 * l)) & 0xFF];
-                const uint2 ma = iq2_sign_masks((a1a >> (7 * l)) & 127u), mb = iq2_sign_masks((a1b >> (7 * l)) & 127u);
+                const uint2 ea = lds64(K.tab_lane + prmt(a0a, 0u, 0x4440u + l) * K.tab_stride);
+                const uint2 eb = lds64(K.tab_lane + prmt(a0b, 0u, 0x4440u + l) * K.tab_stride);
+                uint32_t mal, mah, mbl, mbh;
+                iq2_sign_bytes((a1a >> (7 * l)) & 127u, mal, mah);
+                iq2_sign_bytes((a1b >> (7 * l)) & 127u, mbl, mbh);
                 const uint32_t x0 = xf[8 * sb + 2 * l], x1 = xf[8 * sb + 2 * l + 1];
                 if (l == 0) {
-                    imma0<false>(pos, ea.x, eb.x, ea.y, eb.y, x0, x1);
-                    imma0<false>(neg, ea.x & ma.x, eb.x & mb.x, ea.y & ma.y, eb.y & mb.y, x0, x1);
+                    imma0<true>(d1, ea.x ^ mal, eb.x ^ mbl, ea.y ^ mah, eb.y ^ mbh, x0, x1);
+                    imma0<false>(d2, mal, mbl, mah, mbh, x0, x1);
                 } else {
-                    imma<false>(pos, ea.x, eb.x, ea.y, eb.y, x0, x1);
-                    imma<false>(neg, ea.x & ma.x, eb.x & mb.x, ea.y & ma.y, eb.y & mb.y, x0, x1);
+                    imma<true>(d1, ea.x ^ mal, eb.x ^ mbl, ea.y ^ mah, eb.y ^ mbh, x0, x1);
+                    imma<false>(d2, mal, mbl, mah, mbh, x0, x1);
                 }
             }
-            sum[sb][0] = join_hi_lo(pos[0] - 2 * neg[0], pos[1] - 2 * neg[1]);
-            sum[sb][1] = join_hi_lo(pos[2] - 2 * neg[2], pos[3] - 2 * neg[3]);
+            sum[sb][0] = fmaf(join_hi_lo(d2[0], d2[1]), 1.f / 255.f, join_hi_lo(d1[0], d1[1]));
+            sum[sb][1] = fmaf(join_hi_lo(d2[2], d2[3]), 1.f / 255.f, join_hi_lo(d1[2], d1[3]));
         }
-        const float sa0 = da * (0.5f + (float)(wa[1] >> 28)) * 0.25f, sa1 = da * (0.5f + (float)(wa[3] >> 28)) * 0.25f;
-        const float sb0 = db * (0.5f + (float)(wb[1] >> 28)) * 0.25f, sb1 = db * (0.5f + (float)(wb[3] >> 28)) * 0.25f;
-        acc[0] += sa0 * (xi.x * sum[0][0]) + sa1 * (xi.y * sum[1][0]);
-        acc[1] += sb0 * (xi.x * sum[0][1]) + sb1 * (xi.y * sum[1][1]);
+        const float sa0 = 0.5f + (float)(wa[1] >> 28), sa1 = 0.5f + (float)(wa[3] >> 28);
+        const float sb0 = 0.5f + (float)(wb[1] >> 28), sb1 = 0.5f + (float)(wb[3] >> 28);
+        acc[0] += (0.25f * xs * da) * (sa0 * sum[0][0] + sa1 * sum[1][0]);
+        acc[1] += (0.25f * xs * db) * (sb0 * sum[0][1] + sb1 * sum[1][1]);
     }
 }
 
@@ -310,12 +413,10 @@ __device__ __forceinline__ void unit_sep(const uint8_t *ua, const uint8_t *ub, u
 // xf: this thread's 64 bytes of x for the unit, block b in xf[2b], xf[2b+1].
 // xw: {xs, -, -, -, X0..X7}: the unit's scale for column c and the integer sums
 // of x over its eight blocks.  acc: rows g, g + 8 of column c.
-__device__ __forceinline__ uint2 lds64(const uint8_t *p) { return *reinterpret_cast<const uint2 *>(p); }
-__device__ __forceinline__ int ubyte(uint32_t v, int i) { return (int)__byte_perm(v, 0, 0x4440 + i); }
 
 template <int TY>
 __device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, uint32_t c, const uint32_t (&xf)[16],
-                                          const float *xw, const uint2 *tab, float (&acc)[2]) {
+                                          const float *xw, const uint2 *tab, uint32_t tab_copies, float (&acc)[2]) {
     const float xs = xw[0];
     if constexpr (TY == T_Q4_K) {
         const uint4 ha = lds128(ua), hb = lds128(ub);
@@ -400,7 +501,7 @@ __device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, 
             uint32_t wa[2], wb[2];  // a0: four codebook indices, a1: four 7-bit sign indices + 4-bit scale
             lds_a2<2>(ua + 2 + 8 * b, wa);
             lds_a2<2>(ub + 2 + 8 * b, wb);
-            const uint2 ea = tab[(wa[0] >> (8 * c)) & 0xFF], eb = tab[(wb[0] >> (8 * c)) & 0xFF];
+            const uint2 ea = tab[((wa[0] >> (8 * c)) & 0xFF) * tab_copies], eb = tab[((wb[0] >> (8 * c)) & 0xFF) * tab_copies];
             const uint2 ma = iq2_sign_masks((wa[1] >> (7 * c)) & 127u), mb = iq2_sign_masks((wb[1] >> (7 * c)) & 127u);
             int pos[4], neg[4];
             imma0<false>(pos, ea.x, eb.x, ea.y, eb.y, xf[2 * b], xf[2 * b + 1]);
@@ -492,51 +593,102 @@ __device__ __forceinline__ void quantize16(const XRaw<XDT> &raw, int (&q)[16], f
     qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
 }
 
-// SEP: one column as hi / lo bytes.  Byte order inside an item:
-//   Q4_K / Q8_0 / IQ2_XXS: k order
-//   Q2_0: register s = k (s, 4+s, 8+s, 12+s), the order the masked code words come in
-// info[unit * 4 + quarter] = {xs of its first block, of its second, sum of x over
-// the first, over the second}.
+// SEP: one column as a hi and a lo byte column.  An item is 8 consecutive k; the
+// 32 items of a 256-wide unit are the 32 lanes of one warp, so the unit's largest
+// magnitude is one warp reduction.  Magnitudes are compared as integers (the bit
+// patterns of non-negative floats order like the floats, and every NaN pattern lies
+// above infinity, so a NaN anywhere in the unit comes out on top and is seen).
+// Rounding: v * inv + (1.5 * 2^23 + 128) lands where the float's low mantissa bits are
+// the integer q + 128 = 256 * hi + (lo + 128): hi is byte 1, lo is byte 0 with its top
+// bit flipped.  Byte order inside a unit: k order, the 16-byte pieces of quarters 2 and
+// 3 swapped in pairs (Q2_0: inside each 16, byte 4s + b holds k = s + 4b, the order the
+// masked code words come in).
+// info[unit * 4 + quarter] = {scale, integer sum of x over the quarter's first 32-wide
+// block, over its second, -}.
+template <int XDT> struct XRaw8 { uint4 v[XDT == DT_F32 ? 2 : 1]; };
+
 template <int TY, int XDT>
-__device__ __forceinline__ void stage_x_bytes(uint8_t *xs, float4 *info, const GemvLayout &L, const void *x,
+__device__ __forceinline__ void stage_x_bytes(uint32_t xs32, uint32_t es, uint32_t info32, const void *x,
                                               uint32_t u_first, uint32_t nu, uint32_t tid) {
-    const uint32_t items = nu * 16;
-    const uint32_t total = (items + 31) & ~31u;  // whole warps, for the shuffles
-    constexpr uint32_t kFlight = 3;              // items a thread has in flight: the loads go out first
-    for (uint32_t base = tid; base < total; base += kFlight * kConsumers) {
-        XRaw<XDT> raw[kFlight];
+    const uint32_t items = nu * 32;
+    constexpr uint32_t kFlight = 4;  // items a thread has in flight: the loads go out first
+    constexpr uint32_t kMagicBits = 0x4B400080u;  // 1.5 * 2^23 + 128 as a float
+    const uint32_t e8 = tid & 31;  // this lane's item inside its unit, the same in every pass
+    const uint32_t c = e8 >> 3;
+    const uint32_t piece_off = c * 64 + ((((e8 >> 1) & 3) ^ (c >> 1)) & 3) * 16;
+    for (uint32_t base = tid; base < items; base += kFlight * kConsumers) {
+        XRaw8<XDT> raw[kFlight];
 #pragma unroll
         for (uint32_t r = 0; r < kFlight; r++) {
             const uint32_t i = base + r * kConsumers;
-            raw[r] = load16<XDT>(x, (size_t)u_first * 256 + (size_t)i * 16, i < items);
+            const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(x) +
+                                                              ((size_t)u_first * 256 + (size_t)i * 8) * (XDT == DT_F32 ? 4 : 2));
+#pragma unroll
+            for (int j = 0; j < (XDT == DT_F32 ? 2 : 1); j++)
+                raw[r].v[j] = i < items ? __ldg(src + j) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (uint32_t r = 0; r < kFlight; r++) {
             const uint32_t i = base + r * kConsumers;
-            if (i >= total) break;  // the same for the whole warp
-            const uint32_t u = i >> 4, c = (i >> 2) & 3, piece = i & 3;  // unit, quarter, 16-k piece of the quarter
-            int q[16], qsum;
-            float scale;
-            quantize16<XDT>(raw[r], q, scale, qsum);
-            if (i >= items) continue;
-            // q + 128 = 256 * hi + (lo + 128): hi is its byte 1, lo its byte 0 with the top bit flipped
-            uint32_t rh[4], rl[4];
+            if (i >= items) break;  // the same for the whole warp: a warp holds one unit
+            float v[8];
+            if constexpr (XDT == DT_F32) {
+                v[0] = __uint_as_float(raw[r].v[0].x); v[1] = __uint_as_float(raw[r].v[0].y);
+                v[2] = __uint_as_float(raw[r].v[0].z); v[3] = __uint_as_float(raw[r].v[0].w);
+                v[4] = __uint_as_float(raw[r].v[1].x); v[5] = __uint_as_float(raw[r].v[1].y);
+                v[6] = __uint_as_float(raw[r].v[1].z); v[7] = __uint_as_float(raw[r].v[1].w);
+            } else {
+                const uint32_t w[4] = {raw[r].v[0].x, raw[r].v[0].y, raw[r].v[0].z, raw[r].v[0].w};
 #pragma unroll
-            for (int w = 0; w < 4; w++) {
-                uint32_t t[4];
+                for (int e = 0; e < 4; e++) {
+                    if constexpr (XDT == DT_F16) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
+                        v[2 * e] = f.x; v[2 * e + 1] = f.y;
+                    } else {
+                        v[2 * e] = __uint_as_float(w[e] << 16);
+                        v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+                    }
+                }
+            }
+            uint32_t mb = 0;
 #pragma unroll
-                for (int b = 0; b < 4; b++) t[b] = (uint32_t)(q[TY == T_Q2_0 ? 4 * b + w : 4 * w + b] + 128);
-                rh[w] = __byte_perm(__byte_perm(t[0], t[1], 0x0051), __byte_perm(t[2], t[3], 0x0051), 0x5410);
-                rl[w] = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410) ^ 0x80808080u;
+            for (int j = 0; j < 8; j++) mb = max(mb, __float_as_uint(v[j]) & 0x7FFFFFFFu);
+            mb = __reduce_max_sync(0xffffffffu, mb);
+            const float amax = __uint_as_float(mb);
+            // amax below 1e-30: the unit counts as zeros (32512 / amax would overflow, and its
+            // products vanish in fp32 anyway); amax infinite: inv = 0, scale = inf; amax a NaN:
+            // both comparisons fail, inv = 0, and the scale is that NaN
+            const float inv = amax > 1e-30f ? __fdividef(kXqMax, amax) : 0.f;
+            const float scale = amax * (1.f / kXqMax);
+            uint32_t t[8], tsum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                t[j] = __float_as_uint(fmaf(v[j], inv, __uint_as_float(kMagicBits)));
+                tsum += t[j];
             }
-            uint8_t *dst = xs + u * kXqUnit + xq_piece_offset(c, piece);
-            *reinterpret_cast<uint4 *>(dst) = make_uint4(rh[0], rh[1], rh[2], rh[3]);
-            *reinterpret_cast<uint4 *>(dst + L.es) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
-            if ((piece & 1) == 0) {
-                float *f = reinterpret_cast<float *>(info + u * 4 + c);
-                f[piece >> 1] = scale;
-                f[2 + (piece >> 1)] = scale * (float)qsum;
+            int qsum = (int)(tsum - 8u * kMagicBits);  // sum of the eight q
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+            const uint32_t u = i >> 5;
+            const uint32_t dst = xs32 + u * kXqUnit + piece_off;
+            if constexpr (TY == T_Q2_0) {
+                // this item is half (e8 & 1) of a 16: bytes 2h, 2h + 1 of each of its four words
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const uint32_t at = dst + 4 * w + 2 * (e8 & 1);
+                    sts16(at, prmt(t[w], t[w + 4], 0x0051u) & 0xFFFFu);
+                    sts16(at + es, (prmt(t[w], t[w + 4], 0x0040u) & 0xFFFFu) ^ 0x8080u);
+                }
+            } else {
+                const uint32_t at = dst + 8 * (e8 & 1);
+                sts64(at, prmt(prmt(t[0], t[1], 0x0051u), prmt(t[2], t[3], 0x0051u), 0x5410u),
+                      prmt(prmt(t[4], t[5], 0x0051u), prmt(t[6], t[7], 0x0051u), 0x5410u));
+                sts64(at + es, prmt(prmt(t[0], t[1], 0x0040u), prmt(t[2], t[3], 0x0040u), 0x5410u) ^ 0x80808080u,
+                      prmt(prmt(t[4], t[5], 0x0040u), prmt(t[6], t[7], 0x0040u), 0x5410u) ^ 0x80808080u);
             }
+            const uint32_t rec = info32 + (u * 4 + c) * 16;
+            if ((e8 & 7) == 0) sts32(rec, __float_as_uint(scale));
+            if ((e8 & 3) == 0) sts32(rec + 4 + ((e8 >> 2) & 1) * 4, (uint32_t)qsum);
         }
     }
 }
@@ -639,7 +791,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     uint8_t *xs = smem + L.xs_off;
     float4 *info = reinterpret_cast<float4 *>(smem + L.info_off);  // SEP: [unit][quarter]; WIDE: [unit][column] x 3
     float *red = reinterpret_cast<float *>(smem + L.red_off);      // [tile in group][warp][16][nc]
-    const uint2 *tab = reinterpret_cast<const uint2 *>(smem + L.tab_off);
+    const uint32_t smem32 = smem_u32(smem);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const uint32_t t0 = (uint32_t)((uint64_t)p.tiles * blockIdx.x / gridDim.x);
@@ -656,10 +808,14 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x < 32) reinterpret_cast<uint32_t *>(smem + kZeroOff)[threadIdx.x] = 0u;
     if constexpr (TY == T_IQ2_XXS) {
-        // the codebook: 256 entries of eight magnitude bytes
+        // The codebook, 256 entries of eight magnitude bytes, every entry `tab_copies`
+        // times side by side: a lane reads copy (lane mod copies), so with 16 copies the
+        // 16 lanes of a 64-bit access hit 16 different bank pairs whatever they look up.
         uint64_t *tw = reinterpret_cast<uint64_t *>(smem + L.tab_off);
-        for (uint32_t i = threadIdx.x; i < 256; i += kGemvThreads) tw[i] = g_iq2xxs_grid[i];
+        const uint32_t sh = 31 - __clz(L.tab_copies);
+        for (uint32_t i = threadIdx.x; i < 256 * L.tab_copies; i += kGemvThreads) tw[i] = g_iq2xxs_grid[i >> sh];
     }
     __syncthreads();
 
@@ -726,17 +882,19 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     }
 
     // ---- consumers
-    pdl_wait();  // activations come from the previous kernel; outputs may still be read by it
-
     const uint32_t tid = threadIdx.x;  // 0 .. kConsumers - 1
     // A wait that gives up marks the warp dead; a dead warp skips further waits but
     // keeps walking the loops, so the barriers among the consumer warps still match.
     bool alive = true;
-    auto wait_full = [&](uint32_t s, uint32_t use) {
+    // `seen`: lane 0 already found the stage complete when it looked ahead during the step before
+    auto wait_full = [&](uint32_t s, uint32_t use, bool seen) {
         bool ok = true;
-        if (alive && lane == 0) ok = mbar_wait(&full[s], use & 1, abort_flag, p.status, kStatusFullTimeout);
+        if (alive && lane == 0 && !seen) ok = mbar_wait(&full[s], use & 1, abort_flag, p.status, kStatusFullTimeout);
         alive = alive && __shfl_sync(0xffffffffu, ok, 0);
     };
+    // has the stage at ring position `q` landed?  (lane 0 asks, before a step's arithmetic,
+    // about the next step's stages, so that the answer is there when the step is over)
+    auto peek_full = [&](const RingPos &q) { return lane == 0 && mbar_test_wait(&full[q.s], q.use & 1); };
     auto consumer_sync = [&]() { named_bar_sync(1, kConsumers); };
 
     // What this thread feeds into column g of the MMA's B operand.
@@ -747,18 +905,41 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     const uint8_t *xs_mine = xs + (SEP ? (g & 1) : g) * L.es + c * 64;
     const uint32_t xs_ustride = kXqUnit;
     const uint32_t xq_swap = (c >> 1) * 16;
+    // the same in shared-window addresses for the one-column path; lanes that feed nothing
+    // read the page of zeros (stride 0) instead of predicating every load
+    const SepConst KC = sep_const<TY>(c, lane, smem32 + L.tab_off, L.tab_copies);
+    const uint32_t stages32 = smem32 + kBarBytes;
+    const uint32_t xbase32 = SEP && x_active ? smem32 + L.xs_off + (g & 1) * L.es + c * 64 : smem32 + kZeroOff;
+    const uint32_t xs_s = xbase32 + xq_swap, xs_t = xbase32 + 16 - xq_swap;
+    const uint32_t xstride32 = SEP && x_active ? kXqUnit : 0u;
+    const uint32_t info_c = smem32 + L.info_off + c * 16;
+    // WIDE: this lane's copy of the IQ2_XXS codebook
+    const uint2 *tab = reinterpret_cast<const uint2 *>(smem + L.tab_off) + (lane & (L.tab_copies - 1));
     RingPos rp;
     uint32_t rot = 0;  // the deal of units to warps rotates from step to step
+    bool seen_a = false, seen_b = false;
+    // Everything up to here, and clearing the first group's partial sums, needs nothing from
+    // the kernel before this one.
+    for (uint32_t i = tid; i < min(L.group, ntl) * kGemvWarps * 16 * L.nc; i += kConsumers) red[i] = 0.f;
+    pdl_wait();  // activations come from the previous kernel; outputs may still be read by it
+    if (G.wait_arrivals) {
+        // x may hold, or derive from, rows other GPUs stored during the exchange launched
+        // before this one: it has to be complete on this GPU before anybody reads x.  The
+        // weights of this launch are already streaming in meanwhile.
+        if (tid == 0) gather_wait(G.wait_arrivals, G.wait_epoch, p.status);
+        named_bar_sync(1, kConsumers);
+    }
     for (uint32_t gb = 0; gb < ntl; gb += L.group) {
         const uint32_t gn = min(L.group, ntl - gb);
-        for (uint32_t i = tid; i < gn * kGemvWarps * 16 * L.nc; i += kConsumers) red[i] = 0.f;
+        if (gb > 0)
+            for (uint32_t i = tid; i < gn * kGemvWarps * 16 * L.nc; i += kConsumers) red[i] = 0.f;
         for (uint32_t j0 = 0; j0 < p.nchunk; j0 += L.panel) {
             const uint32_t j1 = min(j0 + L.panel, p.nchunk);
             const uint32_t pu0 = j0 * p.cb, pnu = min(j1 * p.cb, p.nunit) - pu0;
             if (gb == 0 || L.panel < p.nchunk) {
                 // the previous panel is still being read until every warp gets here
                 if (gb > 0 || j0 > 0) consumer_sync();
-                if constexpr (SEP) stage_x_bytes<TY, XDT>(xs, info, L, p.x, pu0, pnu, tid);
+                if constexpr (SEP) stage_x_bytes<TY, XDT>(smem32 + L.xs_off, L.es, smem32 + L.info_off, p.x, pu0, pnu, tid);
                 else stage_x_wide<TY, XDT>(xs, reinterpret_cast<float *>(info), L, p.x, p.k, pu0, pnu, tid);
             }
             consumer_sync();
@@ -771,12 +952,18 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                     const GemvSeg sg = gemv_segment(p, t0 + tl);
                     tn = min(min(L.tps, gb + gn - tl), sg.tile1 - (t0 + tl));
                     const uint32_t sA = rp.s;
-                    wait_full(rp.s, rp.use);
+                    wait_full(rp.s, rp.use, seen_a);
                     rp.next(L.nstage);
                     const uint32_t sB = rp.s;
                     if (spt == 2) {
-                        wait_full(rp.s, rp.use);
+                        wait_full(rp.s, rp.use, seen_b);
                         rp.next(L.nstage);
+                    }
+                    {   // look ahead at the next step's stage(s)
+                        RingPos q = rp;
+                        seen_a = peek_full(q);
+                        q.next(L.nstage);
+                        seen_b = spt == 2 && peek_full(q);
                     }
                     // rows g and g + 8 of the step's first tile
                     const uint8_t *ra = stages + (size_t)sA * L.stage_bytes + (size_t)g * L.rs;
@@ -791,8 +978,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                     // this warp's units: v = first, first + 8, ... of the step's tn * nu,
                     // unit v being unit v % nu of tile v / nu
                     const uint32_t total = tn * nu;
-                    uint32_t v = (warp + kGemvWarps - rot) & (kGemvWarps - 1);
-                    rot = (rot + total) & (kGemvWarps - 1);
+                    uint32_t v = warp >= rot ? warp - rot : warp + kGemvWarps - rot;
+                    rot = (rot + total) % kGemvWarps;
                     uint32_t ti = 0, u = v;
                     while (u >= nu && ti < tn) { u -= nu; ti++; }
                     while (v < total) {
@@ -802,18 +989,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                         float *dst = red + ((size_t)(tl - gb + cur) * kGemvWarps + warp) * 16 * L.nc;
                         if constexpr (SEP) {
                             float acc[2] = {0.f, 0.f};
+                            const uint32_t ta32 = stages32 + (uint32_t)(ta - stages), tb32 = stages32 + (uint32_t)(tb - stages);
                             do {
-                                uint32_t xf[16];
-                                const uint8_t *xp = xs_mine + (pu + u) * xs_ustride;
-#pragma unroll
-                                for (int q = 0; q < 4; q++) {
-                                    uint4 w4 = make_uint4(0u, 0u, 0u, 0u);
-                                    // quarters 2 and 3 keep their pieces swapped in pairs
-                                    if (x_active) w4 = lds128(xp + (q >> 1) * 32 + ((q & 1) ? 16 - xq_swap : xq_swap));
-                                    xf[4 * q] = w4.x; xf[4 * q + 1] = w4.y; xf[4 * q + 2] = w4.z; xf[4 * q + 3] = w4.w;
-                                }
+                                // quarters 2 and 3 keep their 16-byte pieces swapped in pairs
+                                const uint32_t xo = (pu + u) * xstride32;
+                                const uint4 q0 = lds128(xs_s + xo), q1 = lds128(xs_t + xo);
+                                const uint4 q2 = lds128(xs_s + xo + 32), q3 = lds128(xs_t + xo + 32);
+                                const uint32_t xf[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
+                                                         q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+                                const uint4 xi = lds128(info_c + (pu + u) * 64);
                                 const uint32_t off = (ubase + u) * UB;
-                                unit_sep<TY>(ta + off, tb + off, c, xf, info[(pu + u) * 4 + c], tab, acc);
+                                unit_sep<TY>(ta32 + off, tb32 + off, KC, xf, xi, acc);
                                 v += kGemvWarps;
                                 u += kGemvWarps;
                                 while (u >= nu && v < total) { u -= nu; ti++; }
@@ -839,7 +1025,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
                                 const uint32_t off = (ubase + u) * UB;
                                 // lanes of columns that do not exist read column 0's record; their sums are dropped
                                 const float *xw = reinterpret_cast<const float *>(info) + ((size_t)(pu + u) * 4 + (c < L.nc ? c : 0)) * 12;
-                                unit_wide<TY>(ta + off, tb + off, c, xf, xw, tab, acc);
+                                unit_wide<TY>(ta + off, tb + off, c, xf, xw, tab, L.tab_copies, acc);
                                 v += kGemvWarps;
                                 u += kGemvWarps;
                                 while (u >= nu && v < total) { u -= nu; ti++; }
@@ -862,20 +1048,39 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         // every warp's partials of this group are in: add them in warp order and store
         consumer_sync();
         const uint32_t per_tile = 16 * L.nc;
-        for (uint32_t i = tid; i < gn * per_tile; i += kConsumers) {
-            const uint32_t tl = i / per_tile, r = (i % per_tile) / L.nc, col = i % L.nc;
-            const float *src = red + (size_t)tl * kGemvWarps * per_tile + r * L.nc + col;
-            float sum = 0.f;
+        if (G.nranks == 0) {
+            for (uint32_t i = tid; i < gn * per_tile; i += kConsumers) {
+                const uint32_t tl = i / per_tile, r = (i % per_tile) / L.nc, col = i % L.nc;
+                const float *src = red + (size_t)tl * kGemvWarps * per_tile + r * L.nc + col;
+                float sum = 0.f;
 #pragma unroll
-            for (int w = 0; w < kGemvWarps; w++) sum += src[(size_t)w * per_tile];
-            const GemvSeg sg = gemv_segment(p, t0 + gb + tl);
-            const uint32_t row = (t0 + gb + tl - sg.tile0) * 16 + r;
-            if (row < sg.m) {
-                if (G.nranks == 0) {
-                    sg.out[(size_t)col * sg.m + row] = sum;
+                for (int w = 0; w < kGemvWarps; w++) sum += src[(size_t)w * per_tile];
+                const GemvSeg sg = gemv_segment(p, t0 + gb + tl);
+                const uint32_t row = (t0 + gb + tl - sg.tile0) * 16 + r;
+                if (row < sg.m) sg.out[(size_t)col * sg.m + row] = sum;
+            }
+        } else {
+            // Row shards: an item is four consecutive rows of one column for one rank, stored
+            // as one 16-byte word into that rank's copy of the whole output; the ranks of a
+            // run of rows are taken by different threads so that their stores go out side by side.
+            const uint32_t runs = gn * 4 * L.nc;  // (tile, four-row run, column)
+            for (uint32_t i = tid; i < runs * G.nranks; i += kConsumers) {
+                const uint32_t rk = i / runs, j = i % runs;
+                const uint32_t tl = j / (4 * L.nc), r0 = (j / L.nc) % 4 * 4, col = j % L.nc;
+                const float *src = red + (size_t)tl * kGemvWarps * per_tile + r0 * L.nc + col;
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; w++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) sum[e] += src[(size_t)w * per_tile + e * L.nc];
+                const GemvSeg sg = gemv_segment(p, t0 + gb + tl);
+                const uint32_t row = (t0 + gb + tl - sg.tile0) * 16 + r0;
+                if (row >= sg.m) continue;
+                float *dst = G.out[sg.index][rk] + (size_t)col * G.m_total[sg.index] + G.row_first[sg.index] + row;
+                if (row + 4 <= sg.m && ((uintptr_t)dst & 15) == 0) {
+                    *reinterpret_cast<float4 *>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
                 } else {
-                    const size_t at = (size_t)col * G.m_total[sg.index] + G.row_first[sg.index] + row;
-                    for (uint32_t rk = 0; rk < G.nranks; rk++) G.out[sg.index][rk][at] = sum;
+                    for (uint32_t e = 0; e < 4 && row + e < sg.m; e++) dst[e] = sum[e];
                 }
             }
         }
@@ -884,27 +1089,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
     if (G.nranks) {
         // The stores above must be visible on every GPU before this CTA counts itself in:
         // the barrier orders them before thread 0, whose system-wide fence then covers them.
+        // Nobody waits here: the consumers of the next gathered launch (or okf_gather_wait)
+        // wait for the count.  The last CTA of this launch to get here publishes the count
+        // the local counter will have reached when this exchange is complete.
         consumer_sync();
         if (tid == 0) {
             __threadfence_system();
-            for (uint32_t rk = 0; rk < G.nranks; rk++) atomicAdd_system(G.arrivals[rk], 1u);
-            if (blockIdx.x == 0) {
-                // one CTA stays until every CTA of every rank has counted in here: when the
-                // launch is over, the whole output has arrived.  The wait is bounded.
-                const uint32_t e = *G.epoch + 1;
-                *G.epoch = e;
-                const uint32_t target = e * G.nranks * gridDim.x;
-                const long long t_start = clock64();
-                for (;;) {
-                    uint32_t seen;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(G.arrivals[G.rank]) : "memory");
-                    if ((int32_t)(seen - target) >= 0) break;
-                    if (clock64() - t_start > kWaitCycles) {
-                        if (p.status) atomicExch(p.status, kStatusGatherTimeout);
-                        break;
-                    }
-                    __nanosleep(20);
-                }
+            for (uint32_t rk = 0; rk < G.nranks; rk++)
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(G.arrivals[rk]) : "memory");
+            if (atomicAdd(G.epoch + 1, 1u) == gridDim.x - 1) {
+                G.epoch[0] += G.nranks * gridDim.x;
+                G.epoch[1] = 0u;
             }
         }
     }
@@ -925,8 +1120,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
 // any CTA of the launch gets.
 constexpr uint32_t kSharedBudget = 112 * 1024;
 
-static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, GemvArgs &a,
-                        GemvLayout &L) {
+static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, uint32_t tab_copies,
+                             GemvArgs &a, GemvLayout &L) {
     const uint32_t ub = ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
     L.nc = sep ? 1 : n;
     L.ecols = sep ? 2 : 2 * n;
@@ -936,7 +1131,8 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
     if (L.group < 1) L.group = 1;
     if (L.group > tiles_per_cta) L.group = tiles_per_cta;
     const uint32_t red_bytes = L.group * per_tile;
-    const uint32_t tab_bytes = ty == T_IQ2_XXS ? 256 * 8 : 0;
+    const uint32_t tab_bytes = ty == T_IQ2_XXS ? 256 * 8 * tab_copies : 0;
+    L.tab_copies = tab_copies;
     const uint32_t stage_cap = 46 * 1024;
     const uint32_t row_bytes = nunit * ub;
     const uint32_t xunit = kXqUnit, info_unit = sep ? 64 : 4 * 48;  // per unit: 4 quarters x float4, or 4 columns x 12 words
@@ -1013,6 +1209,25 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
     }
     if (have_fallback) { a = fb_a; L = fb_L; }
     return have_fallback;
+}
+
+// IQ2_XXS: as many side-by-side copies of the codebook as leave room for a plan that
+// keeps all of x resident (16 copies make every look-up free of bank conflicts).
+static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, GemvArgs &a,
+                        GemvLayout &L) {
+    if (ty != T_IQ2_XXS) return gemv_layout_with(ty, nunit, n, sep, tiles_per_cta, 1, a, L);
+    GemvArgs fa = a;
+    GemvLayout fl = L;
+    bool have = false;
+    for (uint32_t copies = 16; copies >= 1; copies /= 2) {
+        GemvArgs ta = a;
+        GemvLayout tl = L;
+        if (!gemv_layout_with(ty, nunit, n, sep, tiles_per_cta, copies, ta, tl)) continue;
+        if (tl.panel == ta.nchunk) { a = ta; L = tl; return true; }
+        if (!have) { fa = ta; fl = tl; have = true; }
+    }
+    if (have) { a = fa; L = fl; }
+    return have;
 }
 
 template <int TY, int XDT, bool SEP>
@@ -1109,6 +1324,8 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         G.nranks = gather->nranks;
         G.rank = gather->rank;
         G.epoch = gather->epoch;
+        G.wait_arrivals = gather->wait_arrivals;
+        G.wait_epoch = gather->wait_epoch;
         for (uint32_t r = 0; r < gather->nranks; r++) G.arrivals[r] = gather->arrivals[r];
     }
     const size_t xsz = xdt == DT_F32 ? 4 : 2;
@@ -1138,9 +1355,23 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         }
         if (e != cudaSuccess) return e;
         if (launches) ++*launches;
+        if (gather) {  // a further pass over columns waits for this pass's exchange
+            G.wait_arrivals = gather->arrivals[gather->rank];
+            G.wait_epoch = gather->epoch;
+        }
         c0 += take;
     }
     return cudaSuccess;
+}
+
+__global__ void gather_wait_kernel(const uint32_t *arrivals, const uint32_t *epoch, int *status) {
+    pdl_wait();
+    gather_wait(arrivals, epoch, status);
+}
+
+cudaError_t launch_gather_wait(const uint32_t *arrivals, const uint32_t *epoch, int *status, cudaStream_t s) {
+    gather_wait_kernel<<<1, 1, 0, s>>>(arrivals, epoch, status);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_gemv_fast(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,

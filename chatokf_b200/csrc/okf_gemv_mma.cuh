@@ -27,6 +27,14 @@ namespace okf {
 // one launch: their tiles are numbered through, segment after segment.
 constexpr int kGemvSegs = 4;
 constexpr int kMaxRanks = 8;
+#ifndef OKF_GEMV_WARPS
+#define OKF_GEMV_WARPS 8
+#endif
+constexpr int kGemvWarps = OKF_GEMV_WARPS;         // consumer warps
+constexpr int kGemvThreads = (kGemvWarps + 1) * 32;  // + one producer warp
+constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
+constexpr uint32_t kSpinLimit = 1u << 16;          // polls when draining on the way out
+constexpr int kStatusFullTimeout = 1, kStatusEmptyTimeout = 2, kStatusGatherTimeout = 4;
 // Row-sharded matrices on several GPUs: every rank stores its rows straight into
 // every rank's copy of the whole output (peer-mapped pointers), counts itself in on
 // every rank, and the launch ends on a rank only when all ranks have counted in.
@@ -36,9 +44,31 @@ struct GemvGather {
     uint32_t row_first[kGemvSegs];         // this rank's first row in it
     float *out[kGemvSegs][kMaxRanks];      // rank r's [n][m_total] buffer as mapped here
     uint32_t *arrivals[kMaxRanks];         // rank r's counter of finished CTAs, as mapped here
-    uint32_t *epoch;                       // local: exchanges started so far on this counter
+    uint32_t *epoch;                       // local, two words: {count the local counter reaches when the exchanges
+                                           // launched so far are complete, CTAs of the running launch that are done}
     uint32_t rank;
+    // The exchange launched before this one (null: none): its local counter and epoch
+    // words.  The consumers wait for it to complete before they read x.
+    const uint32_t *wait_arrivals;
+    const uint32_t *wait_epoch;
 };
+
+// Wait, bounded, until the local arrival counter has reached the count published
+// for the exchanges launched so far.  One thread calls it; returns false on a timeout.
+__device__ __forceinline__ bool gather_wait(const uint32_t *arrivals, const uint32_t *epoch, int *status) {
+    const uint32_t target = *reinterpret_cast<const volatile uint32_t *>(epoch);
+    const long long t_start = clock64();
+    for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrivals) : "memory");
+        if ((int32_t)(seen - target) >= 0) return true;
+        if (clock64() - t_start > kWaitCycles) {
+            if (status) atomicExch(status, kStatusGatherTimeout);
+            return false;
+        }
+        __nanosleep(20);
+    }
+}
 struct GemvArgs {
     const uint8_t *w[kGemvSegs];
     float *out[kGemvSegs];
@@ -68,11 +98,6 @@ __device__ __forceinline__ GemvSeg gemv_segment(const GemvArgs &p, uint32_t tile
     return s;
 }
 
-constexpr int kGemvWarps = 8;                      // consumer warps (a power of two; 16 measured no faster)
-constexpr int kGemvThreads = (kGemvWarps + 1) * 32;  // + one producer warp
-constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
-constexpr uint32_t kSpinLimit = 1u << 16;          // polls when draining on the way out
-constexpr int kStatusFullTimeout = 1, kStatusEmptyTimeout = 2, kStatusGatherTimeout = 4;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -93,6 +118,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// The same question without ever blocking.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)

@@ -47,6 +47,9 @@ struct okf_ctx {
     float *par_out[4];
     bool par_gathers;               // the waiting set stores into every rank's output
     okf::GemvGatherPlan par_gather;
+    // the exchange launched last (local counter and epoch words), which the next gathered
+    // launch or okf_gather_wait waits for; null when there is none
+    const uint32_t *last_arrivals, *last_epoch;
 };
 
 

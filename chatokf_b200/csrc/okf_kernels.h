@@ -28,12 +28,15 @@ bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, 
                           const void *x, int xdt, uint32_t n, int sms);
 // `gather` (may be null): the matrices are row shards of larger ones spread over
 // several GPUs; every rank stores its rows into every rank's whole output through
-// peer-mapped pointers and the launch ends when all ranks' rows have arrived
-// (bounded wait; a timeout is reported in the status word).  `out` is unused then.
+// peer-mapped pointers and counts itself in on every rank; the launch does not wait
+// for the others.  The next gathered launch waits (bounded; a timeout is reported in
+// the status word) for this exchange before it reads x, and launch_gather_wait does
+// the same as a kernel of its own.  `out` is unused then.
 struct GemvGatherPlan {
     uint32_t nranks, rank;
     uint32_t *arrivals[8];  // rank r's counter, as mapped into this process
-    uint32_t *epoch;        // local device word
+    uint32_t *epoch;        // two local device words (see GemvGather)
+    const uint32_t *wait_arrivals, *wait_epoch;  // the exchange launched before this one, or null
     struct {
         uint32_t m_total, row_first;
         float *out[8];      // rank r's [n][m_total] buffer, as mapped into this process
@@ -42,6 +45,10 @@ struct GemvGatherPlan {
 cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, const uint32_t *m, float *const *out,
                               uint32_t k, const void *x, int xdt, uint32_t n, int *status, cudaStream_t s,
                               int sms, int dev, uint64_t *launches, const GemvGatherPlan *gather);
+
+// One thread that waits (bounded) until the local arrival counter has reached the
+// published count of the exchanges launched so far.
+cudaError_t launch_gather_wait(const uint32_t *arrivals, const uint32_t *epoch, int *status, cudaStream_t s);
 
 // Prefill matmul on tcgen05 / tensor memory (okf_gemm_tc.cu), any N.
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n);

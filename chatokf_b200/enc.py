@@ -183,10 +183,16 @@ class CudaEnc:
 
     def gemm_gather(self, w: GGUFTensor, X: torch.Tensor, gather, off: Weights, N: int = 1):
         """okf_gemm_gather: this rank's rows of a row-sharded matrix, stored straight into
-        every rank's output (`gather`: a tp.PeerOutputs slot); N <= 8."""
+        every rank's output (`gather`: a tp.PeerOutputs slot); N <= 8.  The next gathered
+        call waits for this exchange before it reads x; end a chain with gather_wait()."""
         c = self.ctx
         c._check(c.lib.okf_gemm_gather(c.h, int(w.type), off.h, w.offset, w.K, w.M, X.data_ptr(), _DT[X.dtype], int(N),
                                        ctypes.byref(gather), _stream_ptr(self.stream)), "okf_gemm_gather")
+
+    def gather_wait(self):
+        """okf_gather_wait: what follows on the stream sees the last gathered output whole."""
+        c = self.ctx
+        c._check(c.lib.okf_gather_wait(c.h, _stream_ptr(self.stream)), "okf_gather_wait")
 
     def gemmTile(self, w: GGUFTensor, X: torch.Tensor, out: torch.Tensor, off: Weights, N: int):
         """MetalEnc.gemmTile: the tensor-core tile at any N (kernel bench)."""

@@ -118,8 +118,8 @@ class PeerOutputs:
             ctx._check(lib.okf_shared_alloc(ctx.h, nbytes, ctypes.byref(p), ctypes.byref(h)), "okf_shared_alloc")
             self._mine.append(p.value)
             handles.append(bytes(h.bytes))
-        # the library's own word per slot: how many exchanges it has started
-        self.epochs = torch.zeros(len(sizes), dtype=torch.int32, device=f"cuda:{ctx.device}")
+        # the library's own two words per slot (okf_gather.epoch)
+        self.epochs = torch.zeros(2 * len(sizes), dtype=torch.int32, device=f"cuda:{ctx.device}")
         everyone = [None] * self.world
         dist.all_gather_object(everyone, handles, group=group)
         self._opened = []
@@ -150,7 +150,7 @@ class PeerOutputs:
             for r in range(self.world):
                 g.out[r] = self.out_base[r] + self.offs[i]
                 g.arrivals[r] = self.cnt_base[r] + 4 * i
-            g.epoch = self.epochs.data_ptr() + 4 * i
+            g.epoch = self.epochs.data_ptr() + 8 * i
             self._slots[key] = g
         return self._slots[key]
 

@@ -136,11 +136,19 @@ OKF_API int okf_parallel_end(okf_ctx *ctx);
  * m_total; every rank computes its rows and the whole output is needed on every
  * rank.  okf_gemm_gather does both in one kernel: each rank stores its rows
  * straight into every rank's copy of the output (pointers mapped from the other
- * processes, plain stores over NVLink) and counts itself in on every rank; the
- * launch on a rank ends when all ranks have counted in there, so whatever follows
- * it on the stream sees the whole output.  That wait is bounded (about a
- * second): if a rank never arrives, the launch ends anyway and
- * okf_device_status reports 4.
+ * processes, plain 16-byte stores over NVLink) and then counts itself in on
+ * every rank.  The launch does not wait for the other ranks.  Whoever reads the
+ * gathered output waits instead:
+ *   - the next okf_gemm_gather call of the context waits, inside its kernel and
+ *     before it reads x, until the exchange launched before it is complete on
+ *     this GPU (its own weights are already streaming in meanwhile);
+ *   - okf_gather_wait enqueues that wait as a kernel of its own, for any other
+ *     reader (another library's kernel, a copy to the host).
+ * So a chain of gathered matvecs needs one okf_gather_wait at its end.  Every
+ * wait is bounded (about a second): if a rank never arrives, the waiting kernel
+ * carries on and okf_device_status reports 4.  The calls of one context must be
+ * issued in the order they run on the GPU (one stream, or streams ordered by
+ * events), since the context remembers which exchange came last.
  *
  * Buffers other ranks write into come from okf_shared_alloc (zero-filled), whose
  * handle another process on the same machine turns into a pointer with
@@ -156,7 +164,7 @@ typedef struct okf_gather {
     uint32_t row_first;      /* first of this rank's rows */
     float *out[8];           /* rank r's [N][m_total] output, as mapped into this process */
     uint32_t *arrivals[8];   /* rank r's arrival counter for this matrix (4 bytes, shared), as mapped here */
-    uint32_t *epoch;         /* 4 bytes of this rank's own device memory, zero at start, used by the library */
+    uint32_t *epoch;         /* 8 bytes of this rank's own device memory per counter, zero at start, used by the library */
 } okf_gather;
 OKF_API int okf_shared_alloc(okf_ctx *ctx, size_t bytes, void **device_ptr, okf_ipc_handle *handle);
 OKF_API int okf_shared_open(okf_ctx *ctx, const okf_ipc_handle *handle, void **device_ptr);
@@ -166,6 +174,9 @@ OKF_API int okf_shared_free(okf_ctx *ctx, void *device_ptr);
 OKF_API int okf_copy_to_host(okf_ctx *ctx, const void *device_ptr, void *host, size_t bytes);
 OKF_API int okf_gemm_gather(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
                             const void *x, int xdt, uint32_t n, const okf_gather *g, okf_stream stream);
+/* Enqueue a wait for the exchange this context launched last (nothing if there is
+ * none): work that follows on `stream` sees the whole gathered output. */
+OKF_API int okf_gather_wait(okf_ctx *ctx, okf_stream stream);
 
 /* Same contract as okf_gemm but always the tensor-core tile, whatever N is.
  * Replaces MetalEnc.gemmTile (Base/MetalEnc.swift:326-352), which the

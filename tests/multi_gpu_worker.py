@@ -40,13 +40,20 @@ def main():
         lo, hi = tp.shard_bounds(m, rank, world)
         shards.append((GGUFTensor(f"w{i}", (k, hi - lo), ty), ctx.upload(tp.shard_rows(ty, blocks, k, m, rank, world))))
         xs.append(torch.from_numpy(X).cuda())
-    for rounds in range(3):  # the counters keep counting from exchange to exchange
-        # matrices 0 and 1 multiply the same x: one launch, one exchange
-        with enc.parallel():
+    for rounds in range(4):  # the counters keep counting from exchange to exchange
+        # Matrices 0 and 1 multiply the same x.  Even rounds: one launch, one exchange on
+        # matrix 0's counter.  Odd rounds: each alone, so the same counter sees exchanges of
+        # another grid size (the count an exchange completes at is a running total).
+        if rounds % 2 == 0:
+            with enc.parallel():
+                for i in (0, 1):
+                    enc.gemm_gather(shards[i][0], xs[0], peers.slot(i, shards[i][0].M), shards[i][1], 1)
+        else:
             for i in (0, 1):
                 enc.gemm_gather(shards[i][0], xs[0], peers.slot(i, shards[i][0].M), shards[i][1], 1)
         for i in range(2, len(cases)):
             enc.gemm_gather(shards[i][0], xs[i], peers.slot(i, shards[i][0].M), shards[i][1], cases[i][3])
+        enc.gather_wait()  # every launch waited for the one before it; this waits for the last
         torch.cuda.synchronize()
         dist.barrier()  # nobody starts the next round while a rank may still read this one
         for i in range(len(cases)):

@@ -24,8 +24,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_peer_that_never_arrives_times_out_and_data_is_in_place():
     """nranks = 2 with both ranks' buffers on this GPU and nobody playing rank 1:
-    the rows are stored into both copies, the wait gives up after about a second,
-    the status word says so and the context stays usable."""
+    the rows are stored into both copies and the launch ends without waiting; the wait
+    that follows gives up after about a second, the status word says so and the
+    context stays usable."""
     ctx = Context(0)  # its own status word
     enc = CudaEnc(ctx)
     ty, k, m_total = GGUFType.Q4_K, 1024, 512
@@ -36,26 +37,49 @@ def test_peer_that_never_arrives_times_out_and_data_is_in_place():
     rb = blocks.view(np.uint8).reshape(-1).size // m_total
     shard0 = ctx.upload(blocks.view(np.uint8).reshape(-1)[: rb * m])
     outs = [torch.full((m_total,), float("nan"), device="cuda") for _ in range(2)]
-    counters = torch.zeros(3, dtype=torch.int32, device="cuda")  # two arrival counters and the epoch
+    counters = torch.zeros(4, dtype=torch.int32, device="cuda")  # two arrival counters and the two epoch words
     g = _lib.Gather()
     g.nranks, g.rank, g.m_total, g.row_first = 2, 0, m_total, 0
     for r in range(2):
         g.out[r] = outs[r].data_ptr()
         g.arrivals[r] = counters.data_ptr() + 4 * r
     g.epoch = counters.data_ptr() + 8
-    enc.gemm_gather(GGUFTensor("w", (k, m), ty), torch.from_numpy(x).cuda(), g, shard0, 1)
+    xd = torch.from_numpy(x).cuda()
+    enc.gemm_gather(GGUFTensor("w", (k, m), ty), xd, g, shard0, 1)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0  # nobody has waited yet
+    grid = int(counters.cpu()[0])    # every CTA of this rank counted itself in on both counters
+    assert grid > 0 and counters.cpu().tolist() == [grid, grid, 2 * grid, 0]
+    enc.gather_wait()
     torch.cuda.synchronize()
     assert ctx.device_status() == 4
     for o in outs:
         got = o.cpu().numpy()
         assert rel_err(got[:m], ref[:m]) <= 1e-4
         assert np.isnan(got[m:]).all()  # the other rank's rows were never written
-    assert counters.cpu().tolist()[2] == 1
-    # the context still works
+    # a second gathered call, standing in for rank 1, completes both exchanges' count: no wait gives up
+    ctx2 = Context(0)
+    enc2 = CudaEnc(ctx2)
+    shard1 = ctx2.upload(blocks.view(np.uint8).reshape(-1)[rb * m:])
+    g1 = _lib.Gather()
+    g1.nranks, g1.rank, g1.m_total, g1.row_first = 2, 1, m_total, m
+    scratch = torch.zeros(2, dtype=torch.int32, device="cuda")
+    for r in range(2):
+        g1.out[r] = outs[r].data_ptr()
+        g1.arrivals[r] = counters.data_ptr() + 4 * r
+    g1.epoch = scratch.data_ptr()
+    enc2.gemm_gather(GGUFTensor("w", (k, m), ty), xd, g1, shard1, 1)
+    enc2.gather_wait()
+    torch.cuda.synchronize()
+    assert ctx2.device_status() == 0
+    for o in outs:
+        assert rel_err(o.cpu().numpy(), ref) <= 1e-4
+    # the first context still works
     out = torch.empty(m, device="cuda")
-    enc.gemv(GGUFTensor("w", (k, m), ty), torch.from_numpy(x).cuda(), out, shard0)
+    enc.gemv(GGUFTensor("w", (k, m), ty), xd, out, shard0)
     torch.cuda.synchronize()
     assert rel_err(out.cpu().numpy(), ref[:m]) <= 1e-4
+    ctx2.close()
 
 
 def test_gather_argument_checks(ctx):
