@@ -162,6 +162,13 @@ class PeerOutputs:
                                                       host.ctypes.data, host.nbytes), "okf_copy_to_host")
         return host
 
+    def read_into(self, i: int, host: torch.Tensor):
+        """Copy this rank's copy of output slot i into a host tensor of the same size."""
+        n, m_total = self.sizes[i]
+        assert host.numel() * host.element_size() == n * m_total * 4 and host.is_contiguous()
+        self.ctx._check(self.ctx.lib.okf_copy_to_host(self.ctx.h, self.out_base[self.rank] + self.offs[i],
+                                                      host.data_ptr(), n * m_total * 4), "okf_copy_to_host")
+
     def close(self):
         """Unmap the other ranks' buffers, then (after a barrier) free this rank's."""
         lib = self.ctx.lib
