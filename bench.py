@@ -293,15 +293,23 @@ class Layers:
         if self.gather == "fused":
             from chatokf_b200 import tp
 
-            self.peers = tp.PeerOutputs(ctx, [(n, t.M * world) for t, _, _, _ in self.items])
+            sizes = [(n, t.M * world) for t, _, _, _ in self.items]
+            # free-running: no launch waits for the exchange before it (x here never derives from
+            # a gathered output) and the step ends with one wait that covers them all; ordered:
+            # every launch waits for the exchange launched before it, as a chain of dependent
+            # projections has to
+            self.peers = tp.PeerOutputs(ctx, sizes, free=True)
+            self.peers_ordered = tp.PeerOutputs(ctx, sizes, free=False)
 
     # Projections the reference's engines wrap in one MetalEnc.parallel region
     # (QwenMetalEngine.swift:464-469 gate || up, :691-696 q || k || v): they read the
     # same activations and have no order among themselves.
     REGIONS = ({"q", "k", "v"}, {"gate", "up"})
 
-    def step(self, enc):
+    def step(self, enc, ordered=False):
         import torch.distributed as dist
+
+        peers = (self.peers_ordered if ordered else self.peers) if self.gather == "fused" else None
 
         i, per_layer = 0, len(self.mats)
         while i < len(self.items):
@@ -314,7 +322,7 @@ class Layers:
             def call(idx):
                 t, w, x, out = self.items[idx]
                 if self.gather == "fused":
-                    enc.gemm_gather(t, x, self.peers.slot(idx, t.M), w, self.n)
+                    enc.gemm_gather(t, x, peers.slot(idx, t.M), w, self.n)
                 else:
                     enc.gemm(t, x, out, w, self.n)
 
@@ -579,7 +587,11 @@ def suite_entry(ctx, torch, stream, name, n, pk, steps=20, layers=None, tile=Fal
     if world > 1:
         out["gather"] = L.gather
     if L.gather == "fused" and world > 1:
+        run_o, _ = time_graph(torch, stream, lambda: L.step(enc, ordered=True), steps, 3)
+        ms_o, _, _ = timed_region(torch, stream, run_o, steps, dist)
+        out["ordered_chain"] = {"ms_per_step": ms_o / steps, "GB/s": L.bytes_per_step / (ms_o / steps) / 1e6}
         L.peers.close()
+        L.peers_ordered.close()
     del L
     torch.cuda.empty_cache()
     return out
@@ -670,6 +682,17 @@ def run_ours(args):
     per_launch_bytes = L.bytes_per_step / L.launches_per_step / world
     per_launch_us = ms_step * 1e3 / L.launches_per_step
 
+    ordered = None
+    if world > 1 and L.gather == "fused":
+        # the same step with every launch waiting for the exchange before it
+        run_o, _ = time_graph(torch, stream, lambda: L.step(enc, ordered=True), args.steps, args.warmup)
+        ms_o, _, _, _ = median_region(torch, stream, run_o, args.steps, dist, regions=3)
+        ordered = {"ms_per_step": ms_o / args.steps,
+                   "value": (L.flops_per_step / (ms_o / args.steps) / 1e9) if tensor_bound
+                   else L.bytes_per_step / (ms_o / args.steps) / 1e6,
+                   "note": "every launch waits, before it reads x, for the exchange launched before it: what a chain "
+                           "of dependent projections pays (a few NVLink crossings per launch)"}
+
     e2e_s, h2d, d2h, api = e2e_steps(ctx, L, max(1, min(args.steps, 10)), args.warmup, torch, dist)
     e2e_val = (L.flops_per_step / e2e_s / 1e12) if tensor_bound else (L.bytes_per_step / e2e_s / 1e9)
 
@@ -701,14 +724,17 @@ def run_ours(args):
                 "parallel_regions": "gate || up and q || k || v leave as one launch each, as the "
                                     "reference's engines co-schedule them",
                 "parallelism": (f"rows/{world}, outputs to every rank by " +
-                                {"fused": "stores from the matvec kernel into peer memory, the next launch waiting "
-                                          "for the exchange before it reads x (no collective)",
+                                {"fused": "stores from the matvec kernel into peer memory (no collective); free-running: "
+                                          "x never derives from a gathered output here, so no launch waits for the "
+                                          "exchange before it and the step ends with one wait that covers them all "
+                                          "(`ordered_chain` is the same step with every launch waiting)",
                                  "nccl": "an NCCL all-gather after every launch",
                                  "none": "nothing (compute only)"}[L.gather]) if world > 1 else "single GPU",
                 "cuda_graph": graphed,
                 "regions": {"n": len(all_ms), "steps_each": args.steps, "value_from": "median",
                             "ms_per_step_min": min(all_ms) / args.steps, "ms_per_step_max": max(all_ms) / args.steps}},
         "roofline": roof,
+        "ordered_chain": ordered,
         "parity": parity_rec,
         "e2e": {"value": e2e_val, "unit": "TFLOP/s" if tensor_bound else "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "api": api},

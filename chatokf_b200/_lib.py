@@ -60,7 +60,7 @@ class IpcHandle(ctypes.Structure):
 class Gather(ctypes.Structure):
     """okf_gather"""
     _fields_ = [("nranks", _u32), ("rank", _u32), ("m_total", _u32), ("row_first", _u32),
-                ("out", _vp * 8), ("arrivals", _vp * 8), ("epoch", _vp)]
+                ("out", _vp * 8), ("arrivals", _vp * 8), ("epoch", _vp), ("flags", _u32)]
 
 
 SIGNATURES.update({

@@ -37,10 +37,14 @@ int grow(okf_ctx *ctx, void **buf, size_t *have, size_t need) {
 // A gathered launch waits for the exchange launched before it and becomes the one the
 // next launch waits for.
 void gather_chain(okf_ctx *ctx, GemvGatherPlan &plan) {
-    plan.wait_arrivals = ctx->last_arrivals;
-    plan.wait_epoch = ctx->last_epoch;
+    plan.wait_arrivals = plan.free_running ? nullptr : ctx->last_arrivals;
+    plan.wait_epoch = plan.free_running ? nullptr : ctx->last_epoch;
+    plan.sig_nranks = ctx->sig_nranks;
+    for (uint32_t r = 0; r < ctx->sig_nranks; r++) plan.sig_arrivals[r] = ctx->sig_arrivals[r];
     ctx->last_arrivals = plan.arrivals[plan.rank];
     ctx->last_epoch = plan.epoch;
+    ctx->sig_nranks = plan.nranks;
+    for (uint32_t r = 0; r < plan.nranks; r++) ctx->sig_arrivals[r] = plan.arrivals[r];
 }
 
 // Launch what a parallel region has collected.
@@ -380,6 +384,7 @@ int okf_gemm_gather(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff,
         plan.nranks = gt->nranks;
         plan.rank = gt->rank;
         plan.epoch = gt->epoch;
+        plan.free_running = (gt->flags & OKF_GATHER_FREE) != 0;
         for (uint32_t r = 0; r < gt->nranks; r++) plan.arrivals[r] = gt->arrivals[r];
     }
     plan.seg[i].m_total = gt->m_total;
@@ -406,12 +411,18 @@ int okf_gather_wait(okf_ctx *ctx, okf_stream stream) {
     if (!ctx) return OKF_E_ARG;
     int rc = par_flush(ctx);
     if (rc) return rc;
-    if (!ctx->last_arrivals) return OKF_OK;
+    if (!ctx->last_arrivals && !ctx->sig_nranks) return OKF_OK;
     DeviceGuard g(ctx->device);
     if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
-    cudaError_t e = launch_gather_wait(ctx->last_arrivals, ctx->last_epoch, ctx->dev_status, (cudaStream_t)stream);
+    GemvGatherPlan plan = {};
+    plan.wait_arrivals = ctx->last_arrivals;
+    plan.wait_epoch = ctx->last_epoch;
+    plan.sig_nranks = ctx->sig_nranks;
+    for (uint32_t r = 0; r < ctx->sig_nranks; r++) plan.sig_arrivals[r] = ctx->sig_arrivals[r];
+    cudaError_t e = launch_gather_wait(plan, ctx->dev_status, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e);
     ctx->last_arrivals = ctx->last_epoch = nullptr;
+    ctx->sig_nranks = 0;
     ctx->launches++;
     return OKF_OK;
 }

@@ -781,7 +781,7 @@ struct RingPos {
 };
 
 template <int TY, int XDT, bool SEP>
-__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvLayout L, GemvGather G) {
+__global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, GemvLayout L, GemvGather G) {
     constexpr uint32_t UB = UnitGeom<TY>::bytes;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -815,12 +815,20 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         // 16 lanes of a 64-bit access hit 16 different bank pairs whatever they look up.
         uint64_t *tw = reinterpret_cast<uint64_t *>(smem + L.tab_off);
         const uint32_t sh = 31 - __clz(L.tab_copies);
-        for (uint32_t i = threadIdx.x; i < 256 * L.tab_copies; i += kGemvThreads) tw[i] = g_iq2xxs_grid[i >> sh];
+        for (uint32_t i = threadIdx.x; i < 256 * L.tab_copies; i += blockDim.x) tw[i] = g_iq2xxs_grid[i >> sh];
     }
     __syncthreads();
 
     // Steps are visited in the same order by the producer and the consumers: group
     // by group, inside a group k-chunk by k-chunk, inside that `tps` tiles at a time.
+    if (warp == kGemvWarps + 1) {
+        // ---- present in row-shard launches only: announce the exchange of the launch before
+        if (lane == 0 && blockIdx.x == 0 && G.sig_nranks) {
+            pdl_wait();
+            gather_signal(G.sig_arrivals, G.sig_nranks);
+        }
+        return;
+    }
     if (warp == kGemvWarps) {
         // ---- producer (one thread): weights do not depend on the previous kernel,
         // so it does not wait for it
@@ -1086,23 +1094,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs p, GemvL
         }
         if (gb + L.group < ntl) consumer_sync();  // before the buffer is zeroed again
     }
-    if (G.nranks) {
-        // The stores above must be visible on every GPU before this CTA counts itself in:
-        // the barrier orders them before thread 0, whose system-wide fence then covers them.
-        // Nobody waits here: the consumers of the next gathered launch (or okf_gather_wait)
-        // wait for the count.  The last CTA of this launch to get here publishes the count
-        // the local counter will have reached when this exchange is complete.
-        consumer_sync();
-        if (tid == 0) {
-            __threadfence_system();
-            for (uint32_t rk = 0; rk < G.nranks; rk++)
-                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(G.arrivals[rk]) : "memory");
-            if (atomicAdd(G.epoch + 1, 1u) == gridDim.x - 1) {
-                G.epoch[0] += G.nranks * gridDim.x;
-                G.epoch[1] = 0u;
-            }
-        }
-    }
+    // Row shards: nobody fences or waits here.  The count the local counter has to reach for
+    // the exchanges launched so far goes up by one per rank; whoever waits next reads it after
+    // this kernel is complete.
+    if (G.nranks && blockIdx.x == 0 && tid == 0) G.epoch[0] += G.nranks;
 }
 
 // Shared-memory plan.  Two CTAs share an SM (this launch's and the next one's,
@@ -1244,7 +1239,7 @@ static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
-    cfg.blockDim = dim3(kGemvThreads);
+    cfg.blockDim = dim3(G.nranks ? kGemvThreadsMax : kGemvThreads);
     cfg.dynamicSmemBytes = L.smem_bytes;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -1325,6 +1320,8 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         G.rank = gather->rank;
         G.epoch = gather->epoch;
         G.wait_arrivals = gather->wait_arrivals;
+        G.sig_nranks = gather->sig_nranks;
+        for (uint32_t r = 0; r < gather->sig_nranks; r++) G.sig_arrivals[r] = gather->sig_arrivals[r];
         G.wait_epoch = gather->wait_epoch;
         for (uint32_t r = 0; r < gather->nranks; r++) G.arrivals[r] = gather->arrivals[r];
     }
@@ -1355,22 +1352,30 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         }
         if (e != cudaSuccess) return e;
         if (launches) ++*launches;
-        if (gather) {  // a further pass over columns waits for this pass's exchange
+        if (gather) {  // a further pass over columns announces this pass's exchange and waits for it
             G.wait_arrivals = gather->arrivals[gather->rank];
             G.wait_epoch = gather->epoch;
+            G.sig_nranks = gather->nranks;
+            for (uint32_t r = 0; r < gather->nranks; r++) G.sig_arrivals[r] = gather->arrivals[r];
         }
         c0 += take;
     }
     return cudaSuccess;
 }
 
-__global__ void gather_wait_kernel(const uint32_t *arrivals, const uint32_t *epoch, int *status) {
+__global__ void gather_wait_kernel(GemvGather G, int *status) {
     pdl_wait();
-    gather_wait(arrivals, epoch, status);
+    if (G.sig_nranks) gather_signal(G.sig_arrivals, G.sig_nranks);
+    if (G.wait_arrivals) gather_wait(G.wait_arrivals, G.wait_epoch, status);
 }
 
-cudaError_t launch_gather_wait(const uint32_t *arrivals, const uint32_t *epoch, int *status, cudaStream_t s) {
-    gather_wait_kernel<<<1, 1, 0, s>>>(arrivals, epoch, status);
+cudaError_t launch_gather_wait(const GemvGatherPlan &plan, int *status, cudaStream_t s) {
+    GemvGather G = {};
+    G.wait_arrivals = plan.wait_arrivals;
+    G.wait_epoch = plan.wait_epoch;
+    G.sig_nranks = plan.sig_nranks;
+    for (uint32_t r = 0; r < plan.sig_nranks; r++) G.sig_arrivals[r] = plan.sig_arrivals[r];
+    gather_wait_kernel<<<1, 1, 0, s>>>(G, status);
     return cudaGetLastError();
 }
 

@@ -32,6 +32,7 @@ constexpr int kMaxRanks = 8;
 #endif
 constexpr int kGemvWarps = OKF_GEMV_WARPS;         // consumer warps
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;  // + one producer warp
+constexpr int kGemvThreadsMax = kGemvThreads + 32;    // + one warp that announces the previous exchange (row shards only)
 constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
 constexpr uint32_t kSpinLimit = 1u << 16;          // polls when draining on the way out
 constexpr int kStatusFullTimeout = 1, kStatusEmptyTimeout = 2, kStatusGatherTimeout = 4;
@@ -43,15 +44,30 @@ struct GemvGather {
     uint32_t m_total[kGemvSegs];           // rows of the whole matrix
     uint32_t row_first[kGemvSegs];         // this rank's first row in it
     float *out[kGemvSegs][kMaxRanks];      // rank r's [n][m_total] buffer as mapped here
-    uint32_t *arrivals[kMaxRanks];         // rank r's counter of finished CTAs, as mapped here
+    uint32_t *arrivals[kMaxRanks];         // rank r's arrival counter, as mapped here: one count per rank and exchange
     uint32_t *epoch;                       // local, two words: {count the local counter reaches when the exchanges
-                                           // launched so far are complete, CTAs of the running launch that are done}
+                                           // launched so far are complete, reserved}
     uint32_t rank;
     // The exchange launched before this one (null: none): its local counter and epoch
     // words.  The consumers wait for it to complete before they read x.
     const uint32_t *wait_arrivals;
     const uint32_t *wait_epoch;
+    // The exchange launched before this one whose rows have not been announced yet
+    // (sig_nranks = 0: none): the counters to add 1 to, on every rank.  A system-wide
+    // fence takes microseconds on this part, so the kernel that stores the rows does not
+    // fence; a spare warp of the NEXT launch does, once that kernel is complete and while
+    // the consumers of this launch are already at work.
+    uint32_t *sig_arrivals[kMaxRanks];
+    uint32_t sig_nranks;
 };
+
+// Announce a complete exchange: every store of the kernel that ran it happens before
+// this thread's fence (the kernel is complete), the fence orders them before the counts.
+__device__ __forceinline__ void gather_signal(uint32_t *const *arrivals, uint32_t nranks) {
+    __threadfence_system();
+    for (uint32_t rk = 0; rk < nranks; rk++)
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(arrivals[rk]) : "memory");
+}
 
 // Wait, bounded, until the local arrival counter has reached the count published
 // for the exchanges launched so far.  One thread calls it; returns false on a timeout.

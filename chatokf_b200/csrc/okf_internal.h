@@ -50,6 +50,9 @@ struct okf_ctx {
     // the exchange launched last (local counter and epoch words), which the next gathered
     // launch or okf_gather_wait waits for; null when there is none
     const uint32_t *last_arrivals, *last_epoch;
+    // its counters on every rank while it has not been announced yet (sig_nranks = 0: none pending)
+    uint32_t sig_nranks;
+    uint32_t *sig_arrivals[8];
 };
 
 

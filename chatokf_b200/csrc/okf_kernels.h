@@ -28,15 +28,19 @@ bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, 
                           const void *x, int xdt, uint32_t n, int sms);
 // `gather` (may be null): the matrices are row shards of larger ones spread over
 // several GPUs; every rank stores its rows into every rank's whole output through
-// peer-mapped pointers and counts itself in on every rank; the launch does not wait
-// for the others.  The next gathered launch waits (bounded; a timeout is reported in
-// the status word) for this exchange before it reads x, and launch_gather_wait does
-// the same as a kernel of its own.  `out` is unused then.
+// peer-mapped pointers; the launch neither fences nor waits.  The next gathered launch
+// announces this exchange on every rank (one spare warp, after a system-wide fence) and,
+// unless it is free-running, waits (bounded; a timeout is reported in the status word)
+// for it before it reads x; launch_gather_wait does both as a kernel of its own.
+// `out` is unused then.
 struct GemvGatherPlan {
     uint32_t nranks, rank;
     uint32_t *arrivals[8];  // rank r's counter, as mapped into this process
     uint32_t *epoch;        // two local device words (see GemvGather)
     const uint32_t *wait_arrivals, *wait_epoch;  // the exchange launched before this one, or null
+    bool free_running;      // the caller vouches that x does not depend on an exchange in flight
+    uint32_t sig_nranks;    // the exchange launched before this one that is still to be announced (0: none):
+    uint32_t *sig_arrivals[8];  // its counters on every rank
     struct {
         uint32_t m_total, row_first;
         float *out[8];      // rank r's [n][m_total] buffer, as mapped into this process
@@ -46,9 +50,9 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
                               uint32_t k, const void *x, int xdt, uint32_t n, int *status, cudaStream_t s,
                               int sms, int dev, uint64_t *launches, const GemvGatherPlan *gather);
 
-// One thread that waits (bounded) until the local arrival counter has reached the
-// published count of the exchanges launched so far.
-cudaError_t launch_gather_wait(const uint32_t *arrivals, const uint32_t *epoch, int *status, cudaStream_t s);
+// One thread that announces the exchange still pending in `plan` (sig_*) and waits (bounded)
+// until the local arrival counter has reached the published count (wait_*).
+cudaError_t launch_gather_wait(const GemvGatherPlan &plan, int *status, cudaStream_t s);
 
 // Prefill matmul on tcgen05 / tensor memory (okf_gemm_tc.cu), any N.
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n);

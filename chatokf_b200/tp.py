@@ -99,13 +99,17 @@ class PeerOutputs:
     into directly (okf_gemm_gather), instead of an all-gather after the kernel.
 
     Every rank allocates one shared buffer holding all its output slots plus one
-    arrival counter per slot, publishes the two IPC handles through the process
+    arrival counter, publishes the two IPC handles through the process
     group, and maps every other rank's pair.  `slot(i, m_local)` is the okf_gather
     record of output i for this rank's rows.  All ranks must create the object
     with the same `sizes` and run the same sequence of gathered calls."""
 
-    def __init__(self, ctx, sizes: list[tuple[int, int]], group=None):
+    def __init__(self, ctx, sizes: list[tuple[int, int]], group=None, free: bool = False):
+        """`free`: the slots carry OKF_GATHER_FREE (no launch waits for the exchange before
+        it; the caller ends a batch of calls with CudaEnc.gather_wait())."""
         from . import _lib
+
+        self.free = bool(free)
 
         self.ctx, self.group = ctx, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -113,13 +117,15 @@ class PeerOutputs:
         self.offs, out_bytes = slot_layout(self.sizes)
         lib = ctx.lib
         self._mine, handles = [], []
-        for nbytes in (out_bytes, 4 * len(sizes)):
+        # one arrival counter (and one pair of epoch words) for all slots: a wait on it covers
+        # every exchange launched so far
+        for nbytes in (out_bytes, 256):
             p, h = ctypes.c_void_p(), _lib.IpcHandle()
             ctx._check(lib.okf_shared_alloc(ctx.h, nbytes, ctypes.byref(p), ctypes.byref(h)), "okf_shared_alloc")
             self._mine.append(p.value)
             handles.append(bytes(h.bytes))
-        # the library's own two words per slot (okf_gather.epoch)
-        self.epochs = torch.zeros(2 * len(sizes), dtype=torch.int32, device=f"cuda:{ctx.device}")
+        # the library's own two words for the counter (okf_gather.epoch)
+        self.epochs = torch.zeros(2, dtype=torch.int32, device=f"cuda:{ctx.device}")
         everyone = [None] * self.world
         dist.all_gather_object(everyone, handles, group=group)
         self._opened = []
@@ -149,8 +155,9 @@ class PeerOutputs:
             g.nranks, g.rank, g.m_total, g.row_first = self.world, self.rank, m_total, self.rank * m_local
             for r in range(self.world):
                 g.out[r] = self.out_base[r] + self.offs[i]
-                g.arrivals[r] = self.cnt_base[r] + 4 * i
-            g.epoch = self.epochs.data_ptr() + 8 * i
+                g.arrivals[r] = self.cnt_base[r]
+            g.epoch = self.epochs.data_ptr()
+            g.flags = 1 if self.free else 0
             self._slots[key] = g
         return self._slots[key]
 

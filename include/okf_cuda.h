@@ -136,9 +136,11 @@ OKF_API int okf_parallel_end(okf_ctx *ctx);
  * m_total; every rank computes its rows and the whole output is needed on every
  * rank.  okf_gemm_gather does both in one kernel: each rank stores its rows
  * straight into every rank's copy of the output (pointers mapped from the other
- * processes, plain 16-byte stores over NVLink) and then counts itself in on
- * every rank.  The launch does not wait for the other ranks.  Whoever reads the
- * gathered output waits instead:
+ * processes, plain 16-byte stores over NVLink).  The launch neither fences nor
+ * waits.  The exchange is announced (a system-wide fence, then one count on every
+ * rank's arrival counter) by a spare warp of the context's next gathered launch
+ * or by okf_gather_wait, once the storing kernel is complete, and whoever reads
+ * the gathered output waits for the counts:
  *   - the next okf_gemm_gather call of the context waits, inside its kernel and
  *     before it reads x, until the exchange launched before it is complete on
  *     this GPU (its own weights are already streaming in meanwhile);
@@ -149,6 +151,14 @@ OKF_API int okf_parallel_end(okf_ctx *ctx);
  * carries on and okf_device_status reports 4.  The calls of one context must be
  * issued in the order they run on the GPU (one stream, or streams ordered by
  * events), since the context remembers which exchange came last.
+ *   An exchange costs a few NVLink crossings (the stores, their acknowledgement,
+ * the count), several microseconds that a chain of dependent matvecs pays once per
+ * launch.  A caller whose next x does not depend on rows still in flight (another
+ * sequence of a batch, a projection of the same activations) sets
+ * OKF_GATHER_FREE: that launch does not wait, and the exchange overlaps the
+ * launches that follow.  A wait covers every exchange launched so far on the
+ * counter it waits on, so matrices that share one arrival counter and epoch (as
+ * tp.PeerOutputs sets them up) are all complete after one okf_gather_wait.
  *
  * Buffers other ranks write into come from okf_shared_alloc (zero-filled), whose
  * handle another process on the same machine turns into a pointer with
@@ -163,9 +173,11 @@ typedef struct okf_gather {
     uint32_t m_total;        /* rows of the whole matrix */
     uint32_t row_first;      /* first of this rank's rows */
     float *out[8];           /* rank r's [N][m_total] output, as mapped into this process */
-    uint32_t *arrivals[8];   /* rank r's arrival counter for this matrix (4 bytes, shared), as mapped here */
+    uint32_t *arrivals[8];   /* rank r's arrival counter (4 bytes, shared; one count per rank and exchange), as mapped here */
     uint32_t *epoch;         /* 8 bytes of this rank's own device memory per counter, zero at start, used by the library */
+    uint32_t flags;          /* 0 or OKF_GATHER_FREE */
 } okf_gather;
+#define OKF_GATHER_FREE 1u   /* x does not depend on an exchange in flight: do not wait for the one before */
 OKF_API int okf_shared_alloc(okf_ctx *ctx, size_t bytes, void **device_ptr, okf_ipc_handle *handle);
 OKF_API int okf_shared_open(okf_ctx *ctx, const okf_ipc_handle *handle, void **device_ptr);
 OKF_API int okf_shared_close(okf_ctx *ctx, void *device_ptr);

@@ -30,7 +30,8 @@ def main():
     enc = CudaEnc(ctx)
     cases = [(GGUFType.Q4_K, 2560, 1024, 1), (GGUFType.Q4_K, 2560, 512, 1), (GGUFType.Q4_K, 1024, 256, 3),
              (GGUFType.IQ2_XXS, 5120, 512, 1), (GGUFType.Q8_0, 2048, 384, 2), (GGUFType.Q2_0, 2048, 640, 1)]
-    peers = tp.PeerOutputs(ctx, [(n, m) for _, _, m, n in cases])
+    # ordered: every launch waits for the exchange before it; free: nobody waits until gather_wait
+    all_peers = [tp.PeerOutputs(ctx, [(n, m) for _, _, m, n in cases], free=f) for f in (False, True)]
     worst = 0.0
     shards, refs, xs = [], [], []
     for i, (ty, k, m, n) in enumerate(cases):
@@ -40,7 +41,8 @@ def main():
         lo, hi = tp.shard_bounds(m, rank, world)
         shards.append((GGUFTensor(f"w{i}", (k, hi - lo), ty), ctx.upload(tp.shard_rows(ty, blocks, k, m, rank, world))))
         xs.append(torch.from_numpy(X).cuda())
-    for rounds in range(4):  # the counters keep counting from exchange to exchange
+    for rounds in range(6):  # the counters keep counting from exchange to exchange
+        peers = all_peers[rounds // 2 % 2]
         # Matrices 0 and 1 multiply the same x.  Even rounds: one launch, one exchange on
         # matrix 0's counter.  Odd rounds: each alone, so the same counter sees exchanges of
         # another grid size (the count an exchange completes at is a running total).
@@ -67,7 +69,8 @@ def main():
     flag = torch.tensor([0 if ok else 1], device="cuda")
     dist.all_reduce(flag)
     torch.cuda.synchronize()
-    peers.close()
+    for peers in all_peers:
+        peers.close()
     # tearing the communicator down has hung on this software stack: leave it to process exit
     os._exit(0 if flag.item() == 0 else 1)
 
