@@ -19,11 +19,11 @@ engine is Swift and cannot be built here, so it is the C restatement in
 oracle/ (kind "port"), row-parallel over all host threads, over the same 64
 layers of distinct weights.
 
-Under torchrun (N > 1) every matrix is split by output rows across the ranks.
-For the decode workloads the matvec kernel itself stores every rank's rows into
-every rank's copy of the output over NVLink and the next launch waits for that
-exchange (okf_gemm_gather); the prefill matmul gathers with an NCCL all-gather.
-Both are inside the timed region.  The total work is fixed, so scaling is
+Under torchrun (N > 1) every matrix is split by output rows across the ranks and
+the kernels themselves store every rank's rows into every rank's copy of the
+output over NVLink (okf_gemm_gather: the matvec's final stores, the matmul's
+epilogue); an NCCL all-gather after the launch is timed beside it.  Every
+exchange completes inside the timed region.  The total work is fixed, so scaling is
 "strong".  Before anything is timed, every rank checks its own gathered copy of
 each distinct matrix's output against the CPU oracle on sampled rows and the
 worst error over all ranks is printed as `parity`.
@@ -283,10 +283,11 @@ class Layers:
         self.bytes_per_step = algorithmic_bytes(mats, xdt, n) * self.layers
         self.weight_bytes_per_step = sum(row_byte_count(ty, k) * m for _, ty, k, m in mats) * self.layers
         self.flops_per_step = sum(2 * n * k * m for _, _, k, m in mats) * self.layers
-        # how the row shards' outputs reach every rank: "fused" = the matvec kernel stores into
-        # every rank's buffer itself (N <= 8), "nccl" = an all-gather after every launch,
+        # how the row shards' outputs reach every rank: "fused" = the kernel stores into every
+        # rank's buffer itself (the matvec's final stores, the matmul's epilogue), "nccl" = an
+        # all-gather after every launch,
         # "none" = not at all (compute only, for comparison)
-        self.gather = gather if (world > 1 and (gather != "fused" or n <= 8)) else ("nccl" if world > 1 else "none")
+        self.gather = gather if world > 1 else "none"
         if world > 1:
             self.gathered = {m: torch.empty(world, n, m, dtype=torch.float32, device="cuda")
                              for m in {mm[3] for mm in self.mats}}
@@ -752,9 +753,10 @@ def run_ours(args):
                     ("q4k_prefill", 512, {"steps": 5}), ("ternary_ffn", 512, {"steps": 5, "layers": 4})]
         else:
             # the configurations that are specified as row-sharded: the IQ2_XXS trunk at batch 1 and 4
-            # (fused exchange) and the 512-token matmul (NCCL all-gather inside the timed region,
-            # and without it for comparison)
+            # and the 512-token matmul with the stores into every rank's output fused into its
+            # epilogue, with an NCCL all-gather after it instead, and without any gather
             plan = [("iq2xxs_trunk", 1, {"layers": 16}), ("iq2xxs_trunk", 4, {"layers": 16}),
+                    ("q4k_prefill", 512, {"steps": 5, "gather": "fused"}),
                     ("q4k_prefill", 512, {"steps": 5, "gather": "nccl"}),
                     ("q4k_prefill", 512, {"steps": 5, "gather": "none"})]
         for name, n, kw in plan:

@@ -127,7 +127,7 @@ int gemm_dispatch(okf_ctx *ctx, int ty, const okf_weights *w, uint64_t woff, uin
             }
         }
         e = launch_gemm_tc(ty, wp, k, m, x, xdt, n, out, odt, ctx->dev_status, ksplit, (float *)ctx->scratch, s,
-                           ctx->sms, ctx->device);
+                           ctx->sms, ctx->device, nullptr);
         if (e == cudaSuccess && ksplit > 1) ctx->launches++;
     } else {
         if (!(ctx->flags & OKF_FLAG_SIMPLE_KERNELS)) ctx->fallbacks++;
@@ -366,8 +366,51 @@ int okf_gemm_gather(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff,
         if (!gt->out[r] || !gt->arrivals[r] || (uintptr_t)gt->out[r] % 16) return OKF_E_ARG;
     int rc = check_gemm_args(ctx, type, w, woff, k, m, x, xdt, n, gt->out[gt->rank], DT_F32);
     if (rc) return rc;
-    if (n > 8) return OKF_E_SHAPE;
     const uint8_t *wp = w->dptr + woff;
+    if (n > 8) {
+        // More than eight tokens: the tensor-core matmul, whose epilogue (or k-range reduction)
+        // stores the tile rows into every rank's output while the other tiles are still in
+        // the tensor cores.  The exchange before it is announced, and unless the call is
+        // free-running waited for, by a one-thread kernel ahead of the matmul.
+        if (!gemm_tc_supported(type, k, m, wp, x, xdt, n)) return OKF_E_ALIGN;
+        if (fault_fires(ctx)) return OKF_E_INJECTED;
+        if ((rc = par_flush(ctx))) return rc;
+        DeviceGuard g(ctx->device);
+        if (!g.ok) return cuda_fail(ctx, cudaErrorInvalidDevice);
+        cudaStream_t s = (cudaStream_t)stream;
+        GemvGatherPlan plan = {};
+        plan.nranks = gt->nranks;
+        plan.rank = gt->rank;
+        plan.epoch = gt->epoch;
+        plan.free_running = (gt->flags & OKF_GATHER_FREE) != 0;
+        for (uint32_t r = 0; r < gt->nranks; r++) {
+            plan.arrivals[r] = gt->arrivals[r];
+            plan.seg[0].out[r] = gt->out[r];
+        }
+        plan.seg[0].m_total = gt->m_total;
+        plan.seg[0].row_first = gt->row_first;
+        gather_chain(ctx, plan);
+        if (plan.sig_nranks || plan.wait_arrivals) {
+            cudaError_t e = launch_gather_wait(plan, ctx->dev_status, s);
+            if (e != cudaSuccess) return cuda_fail(ctx, e);
+            ctx->launches++;
+        }
+        uint32_t ksplit = gemm_tc_ksplit(k, m, n, xdt, ctx->sms);
+        if (ksplit > 1) {
+            const size_t need = (size_t)ksplit * n * m * sizeof(float);
+            if (ctx->scratch_bytes < need) {
+                cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+                (void)cudaStreamIsCapturing(s, &cs);
+                if (cs != cudaStreamCaptureStatusNone) ksplit = 1;
+                else if ((rc = grow(ctx, &ctx->scratch, &ctx->scratch_bytes, need))) return rc;
+            }
+        }
+        cudaError_t e = launch_gemm_tc(type, wp, k, m, x, xdt, n, nullptr, DT_F32, ctx->dev_status, ksplit,
+                                       (float *)ctx->scratch, s, ctx->sms, ctx->device, &plan);
+        if (e != cudaSuccess) return cuda_fail(ctx, e);
+        ctx->launches += ksplit > 1 ? 2 : 1;
+        return OKF_OK;
+    }
     if (!gemv_fast_supported(type, k, m, wp, x, xdt, n, ctx->sms)) return OKF_E_ALIGN;
     if (fault_fires(ctx)) return OKF_E_INJECTED;
     cudaStream_t s = (cudaStream_t)stream;

@@ -24,6 +24,7 @@
 //
 // Every mbarrier wait is bounded (about a second); a wait that gives up records
 // a code in the status word, the CTA frees its tensor memory and returns.
+#include <type_traits>
 #include <cuda.h>
 
 #include <cstring>
@@ -60,6 +61,11 @@ template <int TY, int NACC> struct Rings {
 };
 constexpr int kStatusGemmTimeout = 3;
 
+// Output element type that stands for "fp32, stored into every rank's whole output" (row shards).
+struct GatherF32 { float v; };
+template <typename OT> constexpr bool kIsGather = false;
+template <> constexpr bool kIsGather<GatherF32> = true;
+
 struct Args {
     const uint8_t *w;
     const void *x;
@@ -72,6 +78,16 @@ struct Args {
     // ksplit == 1: the last tail_items (slab, token block) items -- what is left after
     // the full waves -- are cut into tail_parts runs of tail_tok tokens, one per CTA
     uint32_t tail_items, tail_tok, tail_parts;
+};
+// Row shards: where results go instead of Args::out.  `nout` buffers (every rank's copy of
+// the whole output as mapped here), element (token, row) at [token * out_ld + out_row0 + row].
+// A parameter of its own: the main loops compile to slower code (fewer registers, 12 % less
+// throughput measured) when Args grows.
+struct Outs {
+    uint32_t nout, out_ld, out_row0;
+    void *outs[8];
+    uint32_t *epoch;      // the local count the exchange is complete at goes up by epoch_inc
+    uint32_t epoch_inc;
 };
 
 // One piece of work of a CTA: rows [mt * 128, +128) x tokens [n0, n0 + ntok) x k-blocks [kb0, kb1).
@@ -292,7 +308,9 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32
 
 // NACC: token blocks (accumulators) per work item, 1 or 2.
 template <int TY, int XDT, typename OT, int NACC>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __grid_constant__ CUtensorMap xmap) {
+// (The tensor map comes first so that its 128 bytes start on a 128-byte boundary of the
+// parameter block whatever the size of Args: measured 12 % slower when it straddled one.)
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Args p, Outs go) {
     constexpr bool F16 = XDT == DT_F16;
     constexpr bool ASYNC_B = XDT != DT_F32;  // 16-bit activations come by TMA, fp32 ones are converted by eight warps
     using R = Rings<TY, NACC>;
@@ -518,7 +536,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
             const uint32_t n_end = min(p.n, n0 + wk.ntok);
             const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
             const uint32_t row = mt * kBM + q * 32 + lane;
-            OT *out = reinterpret_cast<OT *>(p.out);
             float *part = p.ksplit > 1 ? p.partial + (size_t)wk.part * p.n * p.m : nullptr;
             for (uint32_t a = 0; a < (uint32_t)NACC; a++) {
                 const uint32_t acc = acc0 + a;
@@ -531,14 +548,34 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
                     tmem_ld32(tmem_base + ((q * 32) << 16) + acc * kBN + c0, r);
                     tmem_ld_wait();
                     if (row < p.m) {
+                        if constexpr (!kIsGather<OT>) {
+                            OT *out = reinterpret_cast<OT *>(p.out);
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const uint32_t tok = n0 + a * kBN + c0 + j;
-                            if (tok < n_end) {
-                                const float f = __uint_as_float(r[j]);
-                                if (part) part[(size_t)tok * p.m + row] = f;
-                                else if constexpr (sizeof(OT) == 4) out[(size_t)tok * p.m + row] = f;
-                                else out[(size_t)tok * p.m + row] = __float2bfloat16_rn(f);
+                            for (int j = 0; j < 32; j++) {
+                                const uint32_t tok = n0 + a * kBN + c0 + j;
+                                if (tok < n_end) {
+                                    const float f = __uint_as_float(r[j]);
+                                    if (part) part[(size_t)tok * p.m + row] = f;
+                                    else if constexpr (sizeof(OT) == 4) out[(size_t)tok * p.m + row] = f;
+                                    else out[(size_t)tok * p.m + row] = __float2bfloat16_rn(f);
+                                }
+                            }
+                        } else if (part) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const uint32_t tok = n0 + a * kBN + c0 + j;
+                                if (tok < n_end) part[(size_t)tok * p.m + row] = __uint_as_float(r[j]);
+                            }
+                        } else {
+                            // row shards: a warp stores 32 consecutive rows of one token (128 bytes) into
+                            // every rank's buffer, over NVLink for the other ranks'
+                            for (uint32_t o = 0; o < go.nout; o++) {
+                                float *po = reinterpret_cast<float *>(go.outs[o]) + go.out_row0 + row;
+#pragma unroll
+                                for (int j = 0; j < 32; j++) {
+                                    const uint32_t tok = n0 + a * kBN + c0 + j;
+                                    if (tok < n_end) po[(size_t)tok * go.out_ld] = __uint_as_float(r[j]);
+                                }
                             }
                         }
                     }
@@ -550,6 +587,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(Args p, const __gr
         }
     }
 done:
+    if constexpr (kIsGather<OT>)
+        if (p.ksplit == 1 && blockIdx.x == 0 && threadIdx.x == 0) go.epoch[0] += go.epoch_inc;
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
@@ -558,32 +597,48 @@ done:
     }
 }
 
-// Sum the k-range partials in a fixed order: out[i] = part[0][i] + part[1][i] + ...
+// Sum the k-range partials in a fixed order: out[i] = part[0][i] + part[1][i] + ..., element
+// i = token * m + row going to [token * out_ld + out_row0 + row] of every output buffer.
+struct ReduceOut {
+    uint32_t nout, m, out_ld, out_row0;
+    void *outs[8];
+    uint32_t *epoch;
+    uint32_t epoch_inc;
+};
 template <typename OT>
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, OT *__restrict__ out,
-                                                            size_t count, uint32_t ksplit) {
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, ReduceOut o, size_t count,
+                                                            uint32_t ksplit) {
     const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
+    const bool vec = (o.m & 3) == 0 && (o.out_ld & 3) == 0 && (o.out_row0 & 3) == 0;
     for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < count; i += stride) {
-        if (i + 4 <= count && (count & 3) == 0) {
+        if (vec) {  // four rows of one token
             float4 s = *reinterpret_cast<const float4 *>(part + i);
             for (uint32_t k = 1; k < ksplit; k++) {
                 const float4 v = *reinterpret_cast<const float4 *>(part + k * count + i);
                 s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
-            if constexpr (sizeof(OT) == 4) *reinterpret_cast<float4 *>(out + i) = s;
-            else {
-                out[i] = __float2bfloat16_rn(s.x); out[i + 1] = __float2bfloat16_rn(s.y);
-                out[i + 2] = __float2bfloat16_rn(s.z); out[i + 3] = __float2bfloat16_rn(s.w);
+            const size_t at = o.out_ld == o.m ? i : (i / o.m) * o.out_ld + o.out_row0 + i % o.m;
+            for (uint32_t b = 0; b < o.nout; b++) {
+                if constexpr (sizeof(OT) == 4) *reinterpret_cast<float4 *>(reinterpret_cast<float *>(o.outs[b]) + at) = s;
+                else {
+                    __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(o.outs[b]) + at;
+                    out[0] = __float2bfloat16_rn(s.x); out[1] = __float2bfloat16_rn(s.y);
+                    out[2] = __float2bfloat16_rn(s.z); out[3] = __float2bfloat16_rn(s.w);
+                }
             }
         } else {
             for (size_t e = i; e < count && e < i + 4; e++) {
                 float s = part[e];
                 for (uint32_t k = 1; k < ksplit; k++) s += part[k * count + e];
-                if constexpr (sizeof(OT) == 4) out[e] = s;
-                else out[e] = __float2bfloat16_rn(s);
+                const size_t at = o.out_ld == o.m ? e : (e / o.m) * o.out_ld + o.out_row0 + e % o.m;
+                for (uint32_t b = 0; b < o.nout; b++) {
+                    if constexpr (sizeof(OT) == 4) reinterpret_cast<float *>(o.outs[b])[at] = s;
+                    else reinterpret_cast<__nv_bfloat16 *>(o.outs[b])[at] = __float2bfloat16_rn(s);
+                }
             }
         }
     }
+    if (o.epoch && blockIdx.x == 0 && threadIdx.x == 0) o.epoch[0] += o.epoch_inc;
 }
 
 // Tensor map of the activations X[n][k] (16-bit elements) for tma_load_tile.  The
@@ -612,7 +667,7 @@ static cudaError_t encode_x_map(CUtensorMap *map, const void *x, uint32_t k, uin
 }
 
 template <int TY, int XDT, typename OT, int NACC>
-static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
+static cudaError_t launch_n(const Args &a, const Outs &go, cudaStream_t s, int sms, int dev) {
     static bool attr_set[64] = {};  // the opt-in is per device
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
@@ -628,35 +683,39 @@ static cudaError_t launch_n(const Args &a, cudaStream_t s, int sms, int dev) {
         cudaError_t me = encode_x_map(&xmap, a.x, a.k, a.n);
         if (me != cudaSuccess) return me;
     }
-    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, Rings<TY, NACC>::smem, s>>>(a, xmap);
+    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, Rings<TY, NACC>::smem, s>>>(xmap, a, go);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || a.ksplit == 1) return e;
     const size_t count = (size_t)a.n * a.m;
-    splitk_reduce_kernel<OT><<<sms * 4, 256, 0, s>>>(a.partial, reinterpret_cast<OT *>(a.out), count, a.ksplit);
+    ReduceOut ro = {go.nout, a.m, go.out_ld, go.out_row0, {}, go.epoch, go.epoch_inc};
+    for (uint32_t o = 0; o < go.nout; o++) ro.outs[o] = go.outs[o];
+    using RT = std::conditional_t<kIsGather<OT>, float, OT>;
+    splitk_reduce_kernel<RT><<<sms * 4, 256, 0, s>>>(a.partial, ro, count, a.ksplit);
     return cudaGetLastError();
 }
 
 template <int TY, int XDT, typename OT>
-static cudaError_t launch(const Args &a, uint32_t nacc, cudaStream_t s, int sms, int dev) {
+static cudaError_t launch(const Args &a, const Outs &go, uint32_t nacc, cudaStream_t s, int sms, int dev) {
     if constexpr (XDT != DT_F32) {
-        if (nacc == 2) return launch_n<TY, XDT, OT, 2>(a, s, sms, dev);
+        if (nacc == 2) return launch_n<TY, XDT, OT, 2>(a, go, s, sms, dev);
     }
-    return launch_n<TY, XDT, OT, 1>(a, s, sms, dev);
+    return launch_n<TY, XDT, OT, 1>(a, go, s, sms, dev);
 }
 
 template <int TY, int XDT>
-static cudaError_t launch_o(const Args &a, uint32_t nacc, int odt, cudaStream_t s, int sms, int dev) {
-    if (odt == DT_F32) return launch<TY, XDT, float>(a, nacc, s, sms, dev);
-    if (odt == DT_BF16) return launch<TY, XDT, __nv_bfloat16>(a, nacc, s, sms, dev);
+static cudaError_t launch_o(const Args &a, const Outs &go, uint32_t nacc, int odt, cudaStream_t s, int sms, int dev) {
+    if (odt == DT_F32 && go.epoch) return launch<TY, XDT, GatherF32>(a, go, nacc, s, sms, dev);
+    if (odt == DT_F32) return launch<TY, XDT, float>(a, go, nacc, s, sms, dev);
+    if (odt == DT_BF16) return launch<TY, XDT, __nv_bfloat16>(a, go, nacc, s, sms, dev);
     return cudaErrorInvalidValue;
 }
 
 template <int TY>
-static cudaError_t launch_x(const Args &a, uint32_t nacc, int xdt, int odt, cudaStream_t s, int sms, int dev) {
+static cudaError_t launch_x(const Args &a, const Outs &go, uint32_t nacc, int xdt, int odt, cudaStream_t s, int sms, int dev) {
     switch (xdt) {
-    case DT_F16: return launch_o<TY, DT_F16>(a, nacc, odt, s, sms, dev);
-    case DT_BF16: return launch_o<TY, DT_BF16>(a, nacc, odt, s, sms, dev);
-    case DT_F32: return launch_o<TY, DT_F32>(a, nacc, odt, s, sms, dev);
+    case DT_F16: return launch_o<TY, DT_F16>(a, go, nacc, odt, s, sms, dev);
+    case DT_BF16: return launch_o<TY, DT_BF16>(a, go, nacc, odt, s, sms, dev);
+    case DT_F32: return launch_o<TY, DT_F32>(a, go, nacc, odt, s, sms, dev);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -721,9 +780,21 @@ bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void
 
 cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
                            uint32_t n, void *out, int odt, int *status, uint32_t ksplit, float *partial,
-                           cudaStream_t s, int sms, int dev) {
-    tc::Args a;
+                           cudaStream_t s, int sms, int dev, const GemvGatherPlan *gather) {
+    tc::Args a = {};
     a.w = w; a.x = x; a.out = out; a.status = status; a.k = k; a.m = m; a.n = n;
+    tc::Outs go = {};
+    if (gather) {
+        // row shards: the epilogue (or the reduction) stores into every rank's whole output
+        go.nout = gather->nranks;
+        go.out_ld = gather->seg[0].m_total;
+        go.out_row0 = gather->seg[0].row_first;
+        for (uint32_t r = 0; r < gather->nranks; r++) go.outs[r] = gather->seg[0].out[r];
+        go.epoch = gather->epoch;
+        go.epoch_inc = gather->nranks;
+    } else {
+        go.nout = 1; go.out_ld = m; go.out_row0 = 0; go.outs[0] = out;
+    }
     // the caller decides whether there is a split (it owns the scratch); the rest is planned here
     const GemmPlan plan = gemm_tc_plan(k, m, n, xdt, sms, ksplit > 1 && partial ? ksplit : 1);
     a.ksplit = plan.ksplit;
@@ -731,10 +802,10 @@ cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, con
     a.tail_items = plan.tail_items; a.tail_tok = plan.tail_tok; a.tail_parts = plan.tail_parts;
     a.row_bytes = (k / block_elems(ty)) * block_bytes(ty);
     switch (ty) {
-    case T_Q4_K: return tc::launch_x<T_Q4_K>(a, plan.nacc, xdt, odt, s, sms, dev);
-    case T_Q8_0: return tc::launch_x<T_Q8_0>(a, plan.nacc, xdt, odt, s, sms, dev);
-    case T_Q2_0: return tc::launch_x<T_Q2_0>(a, plan.nacc, xdt, odt, s, sms, dev);
-    case T_IQ2_XXS: return tc::launch_x<T_IQ2_XXS>(a, plan.nacc, xdt, odt, s, sms, dev);
+    case T_Q4_K: return tc::launch_x<T_Q4_K>(a, go, plan.nacc, xdt, odt, s, sms, dev);
+    case T_Q8_0: return tc::launch_x<T_Q8_0>(a, go, plan.nacc, xdt, odt, s, sms, dev);
+    case T_Q2_0: return tc::launch_x<T_Q2_0>(a, go, plan.nacc, xdt, odt, s, sms, dev);
+    case T_IQ2_XXS: return tc::launch_x<T_IQ2_XXS>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -786,7 +857,7 @@ extern "C" int okf_gemm_noalloc(okf_ctx *ctx, int type, const okf_weights *w, ui
     // every (k-range, token, row) slot the reduction reads is written by the main kernel
     // first, so nothing in the array has to be cleared between calls
     cudaError_t e = launch_gemm_tc(type, wp, k, m, x, xdt, n, out, odt, ctx->dev_status, ksplit,
-                                   g_static_scratch_addr[ctx->device], (cudaStream_t)stream, ctx->sms, ctx->device);
+                                   g_static_scratch_addr[ctx->device], (cudaStream_t)stream, ctx->sms, ctx->device, nullptr);
     if (e != cudaSuccess) return cuda_fail(ctx, e);
     ctx->launches += 2;
     return OKF_OK;

@@ -60,8 +60,10 @@ bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void
 // (ksplit * n * m floats) and are summed by a second kernel; gemm_tc_ksplit
 // proposes a split for a shape.
 uint32_t gemm_tc_ksplit(uint32_t k, uint32_t m, uint32_t n, int xdt, int sms);
+// `gather` (may be null): row shards, as for the matvec; results go to every rank's whole
+// output (seg[0]) instead of `out`.
 cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, const void *x, int xdt,
                            uint32_t n, void *out, int odt, int *status, uint32_t ksplit, float *partial,
-                           cudaStream_t s, int sms, int dev);
+                           cudaStream_t s, int sms, int dev, const GemvGatherPlan *gather);
 
 }  // namespace okf

@@ -163,8 +163,11 @@ OKF_API int okf_parallel_end(okf_ctx *ctx);
  * Buffers other ranks write into come from okf_shared_alloc (zero-filled), whose
  * handle another process on the same machine turns into a pointer with
  * okf_shared_open.  All ranks must issue the same sequence of calls with the same
- * shapes.  N <= 8 and fp32 outputs only (the matmul for more tokens gathers with
- * a collective).  A buffer must not be written by the next exchange while a rank
+ * shapes.  fp32 outputs only.  N <= 8 runs the matvec kernels; more tokens run the
+ * tensor-core matmul, whose epilogue stores each finished tile into every rank's
+ * output while the other tiles are still being multiplied, so the transfer
+ * overlaps the arithmetic (K a multiple of 64 and x 16-byte aligned, else
+ * OKF_E_ALIGN).  A buffer must not be written by the next exchange while a rank
  * may still read the previous one: alternate two buffers or order the work. */
 typedef struct okf_ipc_handle { unsigned char bytes[64]; } okf_ipc_handle;
 typedef struct okf_gather {
