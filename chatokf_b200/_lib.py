@@ -73,6 +73,22 @@ SIGNATURES.update({
     "okf_gather_wait": (_ci, [_vp, _vp]),
 })
 
+class SrqSide(ctypes.Structure):
+    """okf_srq_side"""
+    _fields_ = [("scale", ctypes.c_float), ("lo", ctypes.c_float), ("hi", ctypes.c_float)]
+
+
+_f = ctypes.c_float
+SIGNATURES.update({
+    "okf_embed_batch": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _u32, _vp, _vp]),
+    "okf_argmax_rows": (_ci, [_vp, _vp, _u32, _u32, _vp, _vp]),
+    "okf_add_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _f, _u32, _u32, _vp]),
+    "okf_silu_mul": (_ci, [_vp, _vp, _vp, _sz, _vp]),
+    "okf_srq": (_ci, [_vp, _vp, _vp, _sz, ctypes.POINTER(SrqSide), _vp]),
+    "okf_linear": (_ci, [_vp, _ci, _vp, _u64, _u32, _u32, _vp, _u32, _vp, ctypes.POINTER(SrqSide),
+                         ctypes.POINTER(SrqSide), _vp, _vp]),
+})
+
 _lib = None
 
 

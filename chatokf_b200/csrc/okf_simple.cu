@@ -50,6 +50,10 @@ cudaError_t launch_dequant(int ty, const uint8_t *w, uint64_t count, float *out,
     case T_Q4_K: return dequant_t<T_Q4_K>(w, count, out, s);
     case T_IQ2_XXS: return dequant_t<T_IQ2_XXS>(w, count, out, s);
     case T_Q2_0: return dequant_t<T_Q2_0>(w, count, out, s);
+    case T_Q4_0: return dequant_t<T_Q4_0>(w, count, out, s);
+    case T_IQ4_NL: return dequant_t<T_IQ4_NL>(w, count, out, s);
+    case T_Q5_K: return dequant_t<T_Q5_K>(w, count, out, s);
+    case T_Q6_K: return dequant_t<T_Q6_K>(w, count, out, s);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -122,6 +126,10 @@ cudaError_t launch_gemv_simple(int ty, const uint8_t *w, uint32_t k, uint32_t m,
     case T_Q4_K: return gemv_simple_t<T_Q4_K>(w, k, m, x, xdt, n, out, s);
     case T_IQ2_XXS: return gemv_simple_t<T_IQ2_XXS>(w, k, m, x, xdt, n, out, s);
     case T_Q2_0: return gemv_simple_t<T_Q2_0>(w, k, m, x, xdt, n, out, s);
+    case T_Q4_0: return gemv_simple_t<T_Q4_0>(w, k, m, x, xdt, n, out, s);
+    case T_IQ4_NL: return gemv_simple_t<T_IQ4_NL>(w, k, m, x, xdt, n, out, s);
+    case T_Q5_K: return gemv_simple_t<T_Q5_K>(w, k, m, x, xdt, n, out, s);
+    case T_Q6_K: return gemv_simple_t<T_Q6_K>(w, k, m, x, xdt, n, out, s);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -225,6 +233,10 @@ cudaError_t launch_gemm_simple(int ty, const uint8_t *w, uint32_t k, uint32_t m,
     case T_Q4_K: return gemm_simple_t<T_Q4_K>(w, k, m, x, xdt, n, out, odt, s);
     case T_IQ2_XXS: return gemm_simple_t<T_IQ2_XXS>(w, k, m, x, xdt, n, out, odt, s);
     case T_Q2_0: return gemm_simple_t<T_Q2_0>(w, k, m, x, xdt, n, out, odt, s);
+    case T_Q4_0: return gemm_simple_t<T_Q4_0>(w, k, m, x, xdt, n, out, odt, s);
+    case T_IQ4_NL: return gemm_simple_t<T_IQ4_NL>(w, k, m, x, xdt, n, out, odt, s);
+    case T_Q5_K: return gemm_simple_t<T_Q5_K>(w, k, m, x, xdt, n, out, odt, s);
+    case T_Q6_K: return gemm_simple_t<T_Q6_K>(w, k, m, x, xdt, n, out, odt, s);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -212,6 +212,54 @@ class CudaEnc:
                                    out.data_ptr() + out_off_bytes, _stream_ptr(self.stream)), "okf_dequant")
 
 
+    # ---- the linears' neighbours ----------------------------------------------------
+
+    def embedBatch(self, ids: torch.Tensor, off: Weights, out: torch.Tensor, nEmbd: int, N: int, type: int,
+                   rows: int, weight_off: int = 0):
+        """MetalEnc.embedBatch(ids:, weightOff:, out:, nEmbd:, N:, type:): out[n] = row ids[n],
+        unpacked exactly.  `rows` is the height of the embedding matrix (ids are checked against it)."""
+        assert ids.dtype == torch.int32 and out.dtype == torch.float32
+        c = self.ctx
+        c._check(c.lib.okf_embed_batch(c.h, int(type), off.h, int(weight_off), int(nEmbd), int(rows), ids.data_ptr(),
+                                       int(N), out.data_ptr(), _stream_ptr(self.stream)), "okf_embed_batch")
+
+    def argmaxRows(self, x: torch.Tensor, out: torch.Tensor, n: int, rows: int):
+        """MetalEnc.argmaxRows(x:, out:, n:, rows:): ties to the lower index."""
+        assert x.dtype == torch.float32 and out.dtype == torch.int32
+        c = self.ctx
+        c._check(c.lib.okf_argmax_rows(c.h, x.data_ptr(), int(n), int(rows), out.data_ptr(),
+                                       _stream_ptr(self.stream)), "okf_argmax_rows")
+
+    def addRmsnormBatch(self, x: torch.Tensor, r, weight: torch.Tensor, y: torch.Tensor, n: int, rows: int,
+                        eps: float, x_stride: int | None = None, y_stride: int | None = None):
+        """MetalEnc.addRmsnormBatch / rmsnormBatch (r = None): x += r; y = rmsnorm(x) * weight."""
+        c = self.ctx
+        c._check(c.lib.okf_add_rmsnorm(c.h, x.data_ptr(), r.data_ptr() if r is not None else None, weight.data_ptr(),
+                                       y.data_ptr(), int(n), int(rows), float(eps), int(x_stride or n),
+                                       int(y_stride or n), _stream_ptr(self.stream)), "okf_add_rmsnorm")
+
+    def siluMul(self, a: torch.Tensor, b: torch.Tensor, n: int):
+        """MetalEnc.siluMul: a = silu(a) * b."""
+        c = self.ctx
+        c._check(c.lib.okf_silu_mul(c.h, a.data_ptr(), b.data_ptr(), int(n), _stream_ptr(self.stream)), "okf_silu_mul")
+
+    def srq(self, src: torch.Tensor, dst: torch.Tensor, n: int, side):
+        """srqTo / srqInPlace: side = (scale, lo, hi) as SRQ.Side."""
+        c = self.ctx
+        s = _lib.SrqSide(*side)
+        c._check(c.lib.okf_srq(c.h, src.data_ptr(), dst.data_ptr(), int(n), ctypes.byref(s), _stream_ptr(self.stream)),
+                 "okf_srq")
+
+    def linear(self, w: GGUFTensor, X: torch.Tensor, out: torch.Tensor, off: Weights, N: int, srq_in, srq_out,
+               scratch: torch.Tensor | None):
+        """MetalEnc.linear(w, X:, out:, off:, N:, srq:, scratch:): clamp -> gemm -> clamp."""
+        c = self.ctx
+        a, b = _lib.SrqSide(*srq_in), _lib.SrqSide(*srq_out)
+        c._check(c.lib.okf_linear(c.h, int(w.type), off.h, w.offset, w.K, w.M, X.data_ptr(), int(N), out.data_ptr(),
+                                  ctypes.byref(a), ctypes.byref(b), scratch.data_ptr() if scratch is not None else None,
+                                  _stream_ptr(self.stream)), "okf_linear")
+
+
 class QB:
     """Host-buffer operator: QB.matvec / QB.dequant (LLM/Base/Quant.swift:68-77)
     and GQ.matmul (LLM/Gemma/Gemma4Quant.swift:150-170) with numpy fp32 arrays.

@@ -10,9 +10,13 @@ import enum
 
 
 class GGUFType(enum.IntEnum):
+    Q4_0 = 2
     Q8_0 = 8
     Q4_K = 12
+    Q5_K = 13
+    Q6_K = 14
     IQ2_XXS = 16
+    IQ4_NL = 20
     Q2_0 = 42  # PrismML ternary, 128 weights / 34 bytes
 
 
@@ -21,6 +25,10 @@ _GEOM = {
     GGUFType.Q4_K: (256, 144),
     GGUFType.IQ2_XXS: (256, 66),
     GGUFType.Q2_0: (128, 34),
+    GGUFType.Q4_0: (32, 18),
+    GGUFType.IQ4_NL: (32, 18),
+    GGUFType.Q5_K: (256, 176),
+    GGUFType.Q6_K: (256, 210),
 }
 
 

@@ -158,6 +158,105 @@ def ternary_q2_0(rng: np.random.Generator, n_weights: int, group: int = 256,
     return pack_q2_0(tern, d)
 
 
+IQ4_NL_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.float32)
+
+
+def _pack_nibbles_16(q: np.ndarray) -> np.ndarray:
+    """32 four-bit codes per block -> 16 bytes: byte j = code j | code (j + 16) << 4."""
+    q = q.astype(np.uint8).reshape(-1, 2, 16)
+    return q[:, 0, :] | (q[:, 1, :] << 4)
+
+
+def quantize_q4_0(w: np.ndarray) -> np.ndarray:
+    """d = max|w| / 7 per 32 weights, q = round(w / d) + 8 in 0..15."""
+    w = np.asarray(w, dtype=np.float32).reshape(-1, 32)
+    d16 = _f16(np.abs(w).max(axis=1) / 7.0)
+    d = d16.astype(np.float32)[:, None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(d > 0, np.rint(w / d), 0.0)
+    q = np.clip(q + 8, 0, 15)
+    out = np.empty((w.shape[0], 18), dtype=np.uint8)
+    out[:, 0:2] = d16.view(np.uint8).reshape(-1, 2)
+    out[:, 2:] = _pack_nibbles_16(q)
+    return out.reshape(-1)
+
+
+def quantize_iq4_nl(w: np.ndarray) -> np.ndarray:
+    """d = max|w| / 127 per 32 weights, each weight to the nearest of the 16 codebook values."""
+    w = np.asarray(w, dtype=np.float32).reshape(-1, 32)
+    d16 = _f16(np.abs(w).max(axis=1) / 127.0)
+    d = d16.astype(np.float32)[:, None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        t = np.where(d > 0, w / d, 0.0)
+    q = np.abs(t[:, :, None] - IQ4_NL_VALUES[None, None, :]).argmin(axis=2)
+    out = np.empty((w.shape[0], 18), dtype=np.uint8)
+    out[:, 0:2] = d16.view(np.uint8).reshape(-1, 2)
+    out[:, 2:] = _pack_nibbles_16(q)
+    return out.reshape(-1)
+
+
+def quantize_q5_k(w: np.ndarray) -> np.ndarray:
+    """Min/max affine fit per 32-weight sub-block with five-bit codes, 6-bit scales per super-block."""
+    w = np.asarray(w, dtype=np.float32).reshape(-1, 8, 32)
+    lo = np.minimum(w.min(axis=2), 0.0)
+    hi = w.max(axis=2)
+    scale = (hi - lo) / 31.0
+    neg = -lo
+    d16 = _f16(scale.max(axis=1) / 63.0)
+    m16 = _f16(neg.max(axis=1) / 63.0)
+    d = d16.astype(np.float32)[:, None]
+    dm = m16.astype(np.float32)[:, None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.where(d > 0, np.rint(scale / d), 0.0)
+        mn = np.where(dm > 0, np.rint(neg / dm), 0.0)
+    sc = np.clip(sc, 0, 63)
+    mn = np.clip(mn, 0, 63)
+    eff = (d * sc)[:, :, None]
+    off = (dm * mn)[:, :, None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(eff > 0, np.rint((w + off) / eff), 0.0)
+    q = np.clip(q, 0, 31).astype(np.uint8)
+    nb = w.shape[0]
+    out = np.empty((nb, 176), dtype=np.uint8)
+    out[:, 0:2] = d16.view(np.uint8).reshape(-1, 2)
+    out[:, 2:4] = m16.view(np.uint8).reshape(-1, 2)
+    out[:, 4:16] = pack_q4k_scales(sc, mn)
+    # fifth bit of sub-block j is bit j of qh[l]
+    out[:, 16:48] = ((q >> 4) << np.arange(8, dtype=np.uint8)[None, :, None]).sum(axis=1).astype(np.uint8)
+    nib = (q & 15).reshape(nb, 4, 2, 32)  # group g: sub-block 2g in low nibbles, 2g+1 in high
+    out[:, 48:] = (nib[:, :, 0, :] | (nib[:, :, 1, :] << 4)).reshape(nb, 128)
+    return out.reshape(-1)
+
+
+def quantize_q6_k(w: np.ndarray) -> np.ndarray:
+    """Six-bit codes q in 0..63 (weight = d * s * (q - 32)), one int8 scale s per 16 weights."""
+    w = np.asarray(w, dtype=np.float32).reshape(-1, 16, 16)  # block, scale group, element
+    nb = w.shape[0]
+    want = np.abs(w).max(axis=2) / 31.0  # d * s per group
+    d16 = _f16(want.max(axis=1) / 127.0)
+    d = d16.astype(np.float32)[:, None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        s = np.where(d > 0, np.rint(want / d), 0.0)
+    s = np.clip(s, 0, 127)
+    eff = (d * s)[:, :, None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(eff > 0, np.rint(w / eff), 0.0)
+    q = (np.clip(q, -32, 31) + 32).astype(np.uint8).reshape(nb, 2, 4, 32)  # half n, quarter r, l
+    out = np.empty((nb, 210), dtype=np.uint8)
+    lo = q & 15
+    # ql[n*64 + l] = r0 | r2 << 4, ql[n*64 + 32 + l] = r1 | r3 << 4
+    ql = np.empty((nb, 2, 64), dtype=np.uint8)
+    ql[:, :, 0:32] = lo[:, :, 0, :] | (lo[:, :, 2, :] << 4)
+    ql[:, :, 32:64] = lo[:, :, 1, :] | (lo[:, :, 3, :] << 4)
+    out[:, 0:128] = ql.reshape(nb, 128)
+    h = q >> 4
+    out[:, 128:192] = (h[:, :, 0, :] | (h[:, :, 1, :] << 2) | (h[:, :, 2, :] << 4) | (h[:, :, 3, :] << 6)).reshape(nb, 64)
+    # scale index n*8 + 2r + l/16 = the groups in k order
+    out[:, 192:208] = s.astype(np.int8).view(np.uint8)
+    out[:, 208:210] = d16.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
+
+
 def quantize(ty: int, w: np.ndarray) -> np.ndarray:
     """Encode fp32 weights (any shape, K fastest) as blocks of type `ty`."""
     ty = int(ty)
@@ -176,17 +275,26 @@ def quantize(ty: int, w: np.ndarray) -> np.ndarray:
         with np.errstate(divide="ignore", invalid="ignore"):
             c = np.where(d[:, None] > 0, np.rint(ww / d[:, None]), 0.0)
         return pack_q2_0(np.clip(c, -1, 1).astype(np.int8) + 1, d)
+    if ty == GGUFType.Q4_0:
+        return quantize_q4_0(w)
+    if ty == GGUFType.IQ4_NL:
+        return quantize_iq4_nl(w)
+    if ty == GGUFType.Q5_K:
+        return quantize_q5_k(w)
+    if ty == GGUFType.Q6_K:
+        return quantize_q6_k(w)
     raise ValueError(f"no encoder for type {ty}")
 
 
 def random_blocks(ty: int, n_blocks: int, rng: np.random.Generator) -> np.ndarray:
     """Uniformly random payload bytes with a finite, modest fp16 scale: every
-    bit pattern of the payload is a valid block for all four types, so this
+    bit pattern of the payload is a valid block for every type here, so this
     reaches codes a fitted encoder never emits (e.g. ternary code 3)."""
     bb = block_bytes(ty)
     out = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
     d = _f16(rng.normal(0, 0.01, size=n_blocks))
-    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
-    if int(ty) == GGUFType.Q4_K:
+    at = 208 if int(ty) == GGUFType.Q6_K else 0  # Q6_K keeps its scale at the end of the block
+    out[:, at:at + 2] = d.view(np.uint8).reshape(-1, 2)
+    if int(ty) in (GGUFType.Q4_K, GGUFType.Q5_K):
         out[:, 2:4] = _f16(np.abs(rng.normal(0, 0.01, size=n_blocks))).view(np.uint8).reshape(-1, 2)
     return out.reshape(-1)

@@ -38,7 +38,16 @@ typedef enum okf_type {
     OKF_Q8_0 = 8,     /* 34 B / 32 weights   */
     OKF_Q4_K = 12,    /* 144 B / 256 weights */
     OKF_IQ2_XXS = 16, /* 66 B / 256 weights  */
-    OKF_Q2_0 = 42     /* 34 B / 128 weights, ternary */
+    OKF_Q2_0 = 42,    /* 34 B / 128 weights, ternary */
+    /* The rest of the decoder table the trunks' files mix in (Blocks.decoder,
+     * Quantize/Blocks.swift:10-29; Gemma/Gemma4Quant.swift:5-49): the same entry
+     * points take them, bit-exact decode included, on the plain warp-per-row /
+     * fp32-tile kernels (counted by okf_fallback_count), not on the streaming
+     * integer-MMA matvec or the tensor-core tile. */
+    OKF_Q4_0 = 2,     /* 18 B / 32 weights   */
+    OKF_Q5_K = 13,    /* 176 B / 256 weights */
+    OKF_Q6_K = 14,    /* 210 B / 256 weights */
+    OKF_IQ4_NL = 20   /* 18 B / 32 weights, codebook of 16 values */
 } okf_type;
 
 /* element type of activations / outputs */
@@ -228,6 +237,47 @@ OKF_API int okf_gemm_noalloc(okf_ctx *ctx, int type, const okf_weights *w, uint6
 OKF_API int okf_dequant(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint64_t count,
                 float *out, okf_stream stream);
 
+/* ---- the linears' neighbours in the engines' command streams ---------------------
+ * Small memory-bound operators that read or write the same activations as the
+ * quantized linears; all asynchronous on `stream`, device pointers throughout. */
+
+/* out[n][K] = row ids[n] of the embedding matrix (rows x K, any supported type),
+ * unpacked bit for bit as okf_dequant does.  Replaces MetalEnc.embedBatch
+ * (Base/MetalEnc.swift:1096-1147) and QwenEngine.embed (Qwen/QwenEngine.swift:68-76).
+ * An id outside [0, rows) yields a row of zeros and okf_device_status 8. */
+OKF_API int okf_embed_batch(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t rows,
+                            const int32_t *ids, uint32_t n, float *out, okf_stream stream);
+
+/* out[r] = index of the largest of x[r][0..n); ties go to the lower index, NaNs never
+ * win.  Replaces MetalEnc.argmaxRows / argmax_rows (Base/MetalEnc.swift:496-503,
+ * metal/Kernels.metal:2756-2794): a verify step keeps its logits on the device. */
+OKF_API int okf_argmax_rows(okf_ctx *ctx, const float *x, uint32_t n, uint32_t rows, int32_t *out, okf_stream stream);
+
+/* x[row] += r[row] (r may be NULL: plain RMS norm), then y[row] = x[row] * scale * weight
+ * with scale = 1 / sqrt(mean(x[row]^2) + eps); rows are x_stride / y_stride floats apart.
+ * Replaces add_rmsnorm_batch / rmsnorm_batch (metal/Kernels.metal:2811-2864) and
+ * Kernels.rmsnorm (Base/Kernels.swift:12-20).  `weight` is n floats in device memory. */
+OKF_API int okf_add_rmsnorm(okf_ctx *ctx, float *x, const float *r, const float *weight, float *y, uint32_t n,
+                            uint32_t rows, float eps, uint32_t x_stride, uint32_t y_stride, okf_stream stream);
+
+/* a[i] = silu(a[i]) * b[i], silu(v) = v / (1 + exp(-v)): the FFN's gate * up.  Replaces
+ * silu_mul (metal/Kernels.metal:3280-3285; Qwen/QwenEngine.swift:83). */
+OKF_API int okf_silu_mul(okf_ctx *ctx, float *a, const float *b, size_t n, okf_stream stream);
+
+/* One side of gemma's clamp around a linear (SRQ.Side, Gemma/Gemma4Quant.swift:367-377):
+ * scale != 0 -> clamp(round_half_even(x / scale), -128, 127) * scale; else lo < hi -> clamp
+ * to [lo, hi] without rounding; else inactive. */
+typedef struct okf_srq_side { float scale, lo, hi; } okf_srq_side;
+/* dst[i] = bound(src[i]); dst may be src.  Replaces srq_to / srq_inplace
+ * (metal/Kernels.metal:4743-4767), bit for bit SRQ.apply (Gemma4Quant.swift:413-427). */
+OKF_API int okf_srq(okf_ctx *ctx, const float *src, float *dst, size_t n, const okf_srq_side *side, okf_stream stream);
+/* clamp the input into `scratch` (n * K floats; only needed when `in` is active), okf_gemm,
+ * clamp the output in place: MetalEnc.linear (Base/MetalEnc.swift:762-794).  fp32 x and
+ * out.  Three dependent launches: not allowed inside a parallel region (OKF_E_ARG). */
+OKF_API int okf_linear(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint32_t k, uint32_t m,
+                       const float *x, uint32_t n, float *out, const okf_srq_side *in, const okf_srq_side *out_side,
+                       float *scratch, okf_stream stream);
+
 /* Host-buffer twins of the CPU operator: QB.matvec (Base/Quant.swift:68-71),
  * GQ.matmul (Gemma/Gemma4Quant.swift:150-170), QB.dequant (Base/Quant.swift:73-76).
  * x / out are HOST pointers to fp32; each call copies x to the device, runs the
@@ -250,7 +300,9 @@ OKF_API int okf_fault_inject(okf_ctx *ctx, double rate, uint64_t seed);
 /* Waits inside the kernels (on copies landing in shared memory, on other warps)
  * are bounded; one that gives up writes a non-zero code here and the kernel
  * returns early with its outputs incomplete.  Synchronous; call it after the
- * streams that carried the work have been synchronised.  0 = no wait gave up.
+ * streams that carried the work have been synchronised.  0 = no wait gave up
+ * (1, 2, 3: a copy never landed; 4: a rank never arrived; 8: okf_embed_batch met
+ * an id outside the matrix).
  * The role of the reference's command-buffer error check in GPUGate.verdict
  * (Base/MetalGates.swift:144-165). */
 OKF_API int okf_device_status(okf_ctx *ctx, int *out);

@@ -9,7 +9,7 @@
  *
  * Pinning.  The reference ships no known-answer vectors for these codecs (its
  * codec tests compare against ggml re-expansions of model files that are not in
- * its tree).  The Q8_0, Q4_K and IQ2_XXS decoders here are pinned instead
+ * its tree).  The Q8_0, Q4_K, IQ2_XXS, Q4_0, IQ4_NL, Q5_K and Q6_K decoders here are pinned instead
  * against gguf-py 0.19.0's dequantize -- the same ggml arithmetic the
  * reference's LLMTests/IQ1CodecTests.swift:15-102 compares to -- bit for bit on
  * random and edge-case blocks (tests/test_oracle.py, fixtures in
@@ -34,7 +34,7 @@
 #define OKF_API __attribute__((visibility("default")))
 
 /* LLM/Base/GGUF.swift:3-14 */
-enum { T_Q8_0 = 8, T_Q4_K = 12, T_IQ2_XXS = 16, T_Q2_0 = 42 };
+enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ4_NL = 20, T_Q2_0 = 42 };
 
 static inline float h2f(const uint8_t *p) {
     uint16_t bits;
@@ -48,8 +48,12 @@ static inline float h2f(const uint8_t *p) {
 OKF_API int okf_ref_block_elems(int type) {
     switch (type) {
     case T_Q4_K:
+    case T_Q5_K:
+    case T_Q6_K:
     case T_IQ2_XXS: return 256;
     case T_Q2_0: return 128;
+    case T_Q4_0:
+    case T_IQ4_NL:
     case T_Q8_0: return 32;
     default: return 0;
     }
@@ -59,6 +63,10 @@ OKF_API int okf_ref_block_elems(int type) {
 OKF_API int okf_ref_block_bytes(int type) {
     switch (type) {
     case T_Q4_K: return 144;
+    case T_Q5_K: return 176;
+    case T_Q6_K: return 210;
+    case T_Q4_0:
+    case T_IQ4_NL: return 18;
     case T_IQ2_XXS: return 66;
     case T_Q2_0: return 34;
     case T_Q8_0: return 34;
@@ -146,6 +154,74 @@ static void dq_iq2_xxs(const uint8_t *b, float *out) {
     }
 }
 
+/* LLM/Gemma/Gemma4Quant.swift:30-49 (Q4_0.dequant): (Float(nibble) - 8) * d, byte j ->
+ * elements j (low) and j + 16 (high) */
+static void dq_q4_0(const uint8_t *p, float *out) {
+    float d = h2f(p);
+    for (int j = 0; j < 16; j++) {
+        uint8_t b = p[2 + j];
+        out[j] = ((float)(b & 0x0F) - 8) * d;
+        out[j + 16] = ((float)(b >> 4) - 8) * d;
+    }
+}
+
+/* LLM/Gemma/Gemma4Quant.swift:5-28 (IQ4_NL.kvalues / dequant): kvalues[nibble] * d */
+static const float iq4nl_kvalues[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+static void dq_iq4_nl(const uint8_t *p, float *out) {
+    float d = h2f(p);
+    for (int j = 0; j < 16; j++) {
+        uint8_t b = p[2 + j];
+        out[j] = iq4nl_kvalues[b & 0x0F] * d;
+        out[j + 16] = iq4nl_kvalues[b >> 4] * d;
+    }
+}
+
+/* LLM/Quantize/KQuants.swift:127-158 (KQuant.q5K): {d, dmin, scales[12], qh[32] at 16,
+ * qs[128] at 48}; the fifth bit of sub-block j is bit j of qh[l]; d1 * q - o1 */
+static void dq_q5_k(const uint8_t *b, float *out) {
+    float d = h2f(b), dmin = h2f(b + 2);
+    int y = 0, qoff = 48, isc = 0;
+    uint8_t u1 = 1, u2 = 2;
+    for (int g = 0; g < 4; g++) {
+        float s1, m1, s2, m2;
+        q4k_scale_min(b, isc, &s1, &m1);
+        q4k_scale_min(b, isc + 1, &s2, &m2);
+        float d1 = d * s1, o1 = dmin * m1;
+        float d2 = d * s2, o2 = dmin * m2;
+        for (int l = 0; l < 32; l++) {
+            uint8_t q = b[qoff + l], h = b[16 + l];
+            float lo = (float)((q & 0xF) + ((h & u1) ? 16 : 0));
+            float hi = (float)((q >> 4) + ((h & u2) ? 16 : 0));
+            out[y + l] = d1 * lo - o1;
+            out[y + 32 + l] = d2 * hi - o2;
+        }
+        y += 64;
+        qoff += 32;
+        isc += 2;
+        u1 = (uint8_t)(u1 << 2);
+        u2 = (uint8_t)(u2 << 2);
+    }
+}
+
+/* LLM/Quantize/KQuants.swift:160-177 (KQuant.q6K): {ql[128], qh[64] at 128, i8 scales[16]
+ * at 192, f16 d at 208}; d * Float(s) * Float(q - 32), left to right */
+static void dq_q6_k(const uint8_t *b, float *out) {
+    float d = h2f(b + 208);
+    for (int n = 0; n < 2; n++) {
+        for (int l = 0; l < 32; l++) {
+            int h = b[128 + n * 32 + l];
+            int a = b[n * 64 + l], c = b[n * 64 + l + 32];
+            for (int r = 0; r < 4; r++) {
+                int byte = (r % 2) == 0 ? a : c;
+                int nib = r < 2 ? (byte & 0xF) : (byte >> 4);
+                int q = nib | (((h >> (2 * r)) & 3) << 4);
+                int s = (int8_t)b[192 + n * 8 + 2 * r + l / 16];
+                out[n * 128 + r * 32 + l] = d * (float)s * (float)(q - 32);
+            }
+        }
+    }
+}
+
 typedef void (*decode_fn)(const uint8_t *, float *);
 
 /* LLM/Quantize/Blocks.swift:10-29 (Blocks.decoder) plus the two packed types
@@ -156,6 +232,10 @@ static decode_fn decoder(int type) {
     case T_Q4_K: return dq_q4_k;
     case T_IQ2_XXS: return dq_iq2_xxs;
     case T_Q2_0: return dq_q2_0;
+    case T_Q4_0: return dq_q4_0;
+    case T_IQ4_NL: return dq_iq4_nl;
+    case T_Q5_K: return dq_q5_k;
+    case T_Q6_K: return dq_q6_k;
     default: return NULL;
     }
 }
@@ -219,6 +299,38 @@ static float dot_iq2_xxs(const uint8_t *p, const float *x, int faithful) {
     return dot_super(dq_iq2_xxs, p, x, faithful);
 }
 
+static float dot_q5_k(const uint8_t *p, const float *x, int faithful) {
+    return dot_super(dq_q5_k, p, x, faithful);
+}
+static float dot_q6_k(const uint8_t *p, const float *x, int faithful) {
+    return dot_super(dq_q6_k, p, x, faithful);
+}
+
+/* Gemma4Quant.swift:93-103 (GQ.matvec, q4_0 arm): low and high nibble products added in
+ * turn, the block scale after */
+static float dot_q4_0(const uint8_t *p, const float *x, int faithful) {
+    (void)faithful;
+    float acc = 0, d = h2f(p);
+    for (int j = 0; j < 16; j++) {
+        uint8_t b = p[2 + j];
+        acc += ((float)(b & 0x0F) - 8) * x[j];
+        acc += ((float)(b >> 4) - 8) * x[j + 16];
+    }
+    return acc * d;
+}
+
+/* Gemma4Quant.swift:104-114 (GQ.matvec, iq4_nl arm) */
+static float dot_iq4_nl(const uint8_t *p, const float *x, int faithful) {
+    (void)faithful;
+    float acc = 0, d = h2f(p);
+    for (int j = 0; j < 16; j++) {
+        uint8_t b = p[2 + j];
+        acc += iq4nl_kvalues[b & 0x0F] * x[j];
+        acc += iq4nl_kvalues[b >> 4] * x[j + 16];
+    }
+    return acc * d;
+}
+
 typedef float (*dot_fn)(const uint8_t *, const float *, int);
 
 static dot_fn dotter(int type) {
@@ -227,6 +339,10 @@ static dot_fn dotter(int type) {
     case T_Q4_K: return dot_q4_k;
     case T_IQ2_XXS: return dot_iq2_xxs;
     case T_Q2_0: return dot_q2_0;
+    case T_Q4_0: return dot_q4_0;
+    case T_IQ4_NL: return dot_iq4_nl;
+    case T_Q5_K: return dot_q5_k;
+    case T_Q6_K: return dot_q6_k;
     default: return NULL;
     }
 }
@@ -334,15 +450,15 @@ OKF_API int okf_ref_matvec(int type, const void *w, size_t k, size_t m, const fl
     return run_parallel(j, threads);
 }
 
-/* GQ.matmul (Gemma4Quant.swift:150-170): X [N][K] fp32, out[n*M + m].  Q8_0
- * takes the dequant-reuse path; Q4_K, IQ2_XXS and Q2_0 have no batched twin
- * and answer as N independent matvecs. */
+/* GQ.matmul (Gemma4Quant.swift:150-170): X [N][K] fp32, out[n*M + m].  Q8_0 and Q4_0
+ * take the dequant-reuse path; the other types have no batched twin and answer as N
+ * independent matvecs. */
 OKF_API int okf_ref_matmul(int type, const void *w, size_t k, size_t m, const float *x,
                            size_t n, float *out, int threads) {
     job_t j = {0};
     j.type = type; j.w = (const uint8_t *)w;
     j.k = k; j.m = m; j.n = n; j.x = x; j.out = out;
-    j.mode = (type == T_Q8_0) ? 1 : 0;
+    j.mode = (type == T_Q8_0 || type == T_Q4_0) ? 1 : 0;
     return run_parallel(j, threads);
 }
 
@@ -354,4 +470,57 @@ OKF_API int okf_ref_matmul_f64(int type, const void *w, size_t k, size_t m, cons
     j.type = type; j.w = (const uint8_t *)w;
     j.k = k; j.m = m; j.n = n; j.x = x; j.out64 = out; j.mode = 2;
     return run_parallel(j, threads);
+}
+
+/* ---- the linears' neighbours (CPU engine restatements) ---------------------------- */
+
+/* Kernels.rmsnorm (LLM/Base/Kernels.swift:12-20) after the residual add the GPU twin fuses
+ * (add_rmsnorm_batch, LLM/metal/Kernels.metal:2839-2864): x += r (r may be NULL); sequential
+ * fp32 sum of squares; y = x * scale * w, left to right. */
+OKF_API void okf_ref_add_rmsnorm(float *x, const float *r, const float *w, float *y, size_t n, size_t rows,
+                                 float eps, size_t x_stride, size_t y_stride) {
+    for (size_t row = 0; row < rows; row++) {
+        float *xr = x + row * x_stride, *yr = y + row * y_stride;
+        const float *rr = r ? r + row * x_stride : NULL;
+        float ss = 0;
+        for (size_t i = 0; i < n; i++) {
+            if (rr) xr[i] = xr[i] + rr[i];
+            ss += xr[i] * xr[i];
+        }
+        float scale = 1 / sqrtf(ss / (float)n + eps);
+        for (size_t i = 0; i < n; i++) yr[i] = xr[i] * scale * w[i];
+    }
+}
+
+/* QwenEngine.ffn (LLM/Qwen/QwenEngine.swift:78-87): gate[i] = silu(gate[i]) * up[i],
+ * silu(x) = x / (1 + exp(-x)) */
+OKF_API void okf_ref_silu_mul(float *a, const float *b, size_t n) {
+    for (size_t i = 0; i < n; i++) a[i] = a[i] / (1.0f + expf(-a[i])) * b[i];
+}
+
+/* SRQ.apply (LLM/Gemma/Gemma4Quant.swift:413-427) */
+OKF_API void okf_ref_srq(const float *src, float *dst, size_t n, float scale, float lo, float hi) {
+    if (scale != 0) {
+        float inv = 1 / scale;
+        for (size_t i = 0; i < n; i++) {
+            float q = rintf(src[i] * inv); /* round half to even in the default mode */
+            dst[i] = fminf(fmaxf(q, -128), 127) * scale;
+        }
+    } else if (lo < hi) {
+        for (size_t i = 0; i < n; i++) dst[i] = fminf(fmaxf(src[i], lo), hi);
+    } else {
+        for (size_t i = 0; i < n; i++) dst[i] = src[i];
+    }
+}
+
+/* The host arg-max argmax_rows replaces (LLM/metal/Kernels.metal:2754-2794): first largest
+ * value, a strict > so ties keep the lower index and NaNs never win. */
+OKF_API void okf_ref_argmax_rows(const float *x, size_t n, size_t rows, int *out) {
+    for (size_t r = 0; r < rows; r++) {
+        float bv = -INFINITY;
+        int bi = 0;
+        for (size_t i = 0; i < n; i++)
+            if (x[r * n + i] > bv) { bv = x[r * n + i]; bi = (int)i; }
+        out[r] = bi;
+    }
 }

@@ -14,7 +14,9 @@ LIB = HERE / "libokf_oracle.so"
 
 # ggml type ids, LLM/Base/GGUF.swift:3-14
 Q8_0, Q4_K, IQ2_XXS, Q2_0 = 8, 12, 16, 42
-TYPES = {"q8_0": Q8_0, "q4_k": Q4_K, "iq2_xxs": IQ2_XXS, "q2_0": Q2_0}
+Q4_0, Q5_K, Q6_K, IQ4_NL = 2, 13, 14, 20
+TYPES = {"q8_0": Q8_0, "q4_k": Q4_K, "iq2_xxs": IQ2_XXS, "q2_0": Q2_0,
+         "q4_0": Q4_0, "q5_k": Q5_K, "q6_k": Q6_K, "iq4_nl": IQ4_NL}
 
 _lib = None
 
@@ -42,6 +44,15 @@ def lib() -> ctypes.CDLL:
         L.okf_ref_matvec.argtypes = [ci, vp, sz, sz, vp, vp, ci, ci]
         L.okf_ref_matmul.argtypes = [ci, vp, sz, sz, vp, sz, vp, ci]
         L.okf_ref_matmul_f64.argtypes = [ci, vp, sz, sz, vp, sz, vp, ci]
+        cf = ctypes.c_float
+        L.okf_ref_add_rmsnorm.argtypes = [vp, vp, vp, vp, sz, sz, cf, sz, sz]
+        L.okf_ref_add_rmsnorm.restype = None
+        L.okf_ref_silu_mul.argtypes = [vp, vp, sz]
+        L.okf_ref_silu_mul.restype = None
+        L.okf_ref_srq.argtypes = [vp, vp, sz, cf, cf, cf]
+        L.okf_ref_srq.restype = None
+        L.okf_ref_argmax_rows.argtypes = [vp, sz, sz, vp]
+        L.okf_ref_argmax_rows.restype = None
         _lib = L
     return _lib
 
@@ -114,4 +125,37 @@ def matmul_f64(ty: int, w, k: int, m: int, x, n: int = 1, threads: int = 0) -> n
     out = np.empty((n, m), dtype=np.float64)
     if lib().okf_ref_matmul_f64(ty, _ptr(b), k, m, _ptr(xx), n, _ptr(out), _threads(threads)) != 0:
         raise ValueError("okf_ref_matmul_f64 failed")
+    return out
+
+
+def add_rmsnorm(x, r, w, eps: float):
+    """x += r (r may be None), y = rmsnorm(x) * w per row; returns (x after the add, y)."""
+    x = np.array(x, dtype=np.float32, copy=True, ndmin=2)
+    rows, n = x.shape
+    y = np.empty_like(x)
+    rr = None if r is None else np.ascontiguousarray(np.asarray(r, dtype=np.float32).reshape(rows, n))
+    ww = np.ascontiguousarray(w, dtype=np.float32)
+    lib().okf_ref_add_rmsnorm(_ptr(x), None if rr is None else _ptr(rr), _ptr(ww), _ptr(y), n, rows, float(eps), n, n)
+    return x, y
+
+
+def silu_mul(a, b) -> np.ndarray:
+    a = np.array(a, dtype=np.float32, copy=True).reshape(-1)
+    bb = np.ascontiguousarray(b, dtype=np.float32).reshape(-1)
+    lib().okf_ref_silu_mul(_ptr(a), _ptr(bb), a.size)
+    return a
+
+
+def srq(x, scale: float, lo: float, hi: float) -> np.ndarray:
+    src = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    dst = np.empty_like(src)
+    lib().okf_ref_srq(_ptr(src), _ptr(dst), src.size, float(scale), float(lo), float(hi))
+    return dst
+
+
+def argmax_rows(x) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, n = x.shape
+    out = np.empty(rows, dtype=np.int32)
+    lib().okf_ref_argmax_rows(_ptr(x), n, rows, _ptr(out))
     return out

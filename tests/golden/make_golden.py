@@ -3,7 +3,7 @@
 
     python tests/golden/make_golden.py
 
-For Q8_0, Q4_K and IQ2_XXS the expected dequantised values come from gguf-py's
+For Q8_0, Q4_K, IQ2_XXS, Q4_0, IQ4_NL, Q5_K and Q6_K the expected dequantised values come from gguf-py's
 `gguf.quants.dequantize` (ggml's arithmetic, the yardstick the reference's own
 codec tests use: LLM/LLMTests/IQ1CodecTests.swift:15-102).  Q2_0 is a PrismML
 type gguf-py does not know; its expectation is a NumPy restatement of
@@ -48,8 +48,9 @@ def edge_blocks(ty, rng):
             b = np.full(bb, 0 if fill is None else fill, dtype=np.uint8)
             if fill is None:
                 b[:] = rng.integers(0, 256, size=bb, dtype=np.uint8)
-            b[0:2] = f16_bytes(d)
-            if ty == GGUFType.Q4_K:
+            at = 208 if ty == GGUFType.Q6_K else 0
+            b[at:at + 2] = f16_bytes(d)
+            if ty in (GGUFType.Q4_K, GGUFType.Q5_K):
                 b[2:4] = f16_bytes(abs(d) * 0.5 if fill != 0xAA else 65504.0)
             out.append(b)
     if ty == GGUFType.IQ2_XXS:  # sub-scale nibble 0 and 15 in every sub-block
@@ -60,7 +61,13 @@ def edge_blocks(ty, rng):
             w[1::2] = (w[1::2] & 0x0FFFFFFF) | (nib << 28)
             b[2:] = w.view(np.uint8)
             out.append(b)
-    if ty == GGUFType.Q4_K:  # all sixteen scale bytes at their extremes
+    if ty == GGUFType.Q6_K:  # int8 sub-scales at their extremes
+        for fill in (0x00, 0x7F, 0x80, 0xFF):
+            b = rng.integers(0, 256, size=bb, dtype=np.uint8)
+            b[208:210] = f16_bytes(0.011)
+            b[192:208] = fill
+            out.append(b)
+    if ty in (GGUFType.Q4_K, GGUFType.Q5_K):  # all sixteen scale bytes at their extremes
         for fill in (0x00, 0xFF, 0x3F, 0xC0):
             b = rng.integers(0, 256, size=bb, dtype=np.uint8)
             b[0:2] = f16_bytes(0.011)
@@ -82,7 +89,8 @@ def q2_0_dequant_numpy(blocks):
 def expected_dequant(ty, blocks):
     if ty == GGUFType.Q2_0:
         return q2_0_dequant_numpy(blocks)
-    qt = {GGUFType.Q8_0: QT.Q8_0, GGUFType.Q4_K: QT.Q4_K, GGUFType.IQ2_XXS: QT.IQ2_XXS}[ty]
+    qt = {GGUFType.Q8_0: QT.Q8_0, GGUFType.Q4_K: QT.Q4_K, GGUFType.IQ2_XXS: QT.IQ2_XXS, GGUFType.Q4_0: QT.Q4_0,
+          GGUFType.IQ4_NL: QT.IQ4_NL, GGUFType.Q5_K: QT.Q5_K, GGUFType.Q6_K: QT.Q6_K}[ty]
     return quants.dequantize(blocks.reshape(1, -1), qt).reshape(-1).astype(f32)
 
 
@@ -103,6 +111,15 @@ def ref_matvec(ty, blocks, deq, k, m, x):
                 a = f32(0)
                 for j in range(32):
                     a = f32(a + f32(q[j] * xs[j]))
+                part = f32(a * d)
+            elif ty in (GGUFType.Q4_0, GGUFType.IQ4_NL):  # low / high nibble products in turn, then * d
+                d = rows[r, b, 0:2].copy().view(np.float16).astype(f32)[0]
+                qs = rows[r, b, 2:]
+                val = (lambda n: f32(float(n) - 8.0)) if ty == GGUFType.Q4_0 else (lambda n: synth.IQ4_NL_VALUES[n])
+                a = f32(0)
+                for j in range(16):
+                    a = f32(a + f32(val(int(qs[j]) & 15) * xs[j]))
+                    a = f32(a + f32(val(int(qs[j]) >> 4) * xs[j + 16]))
                 part = f32(a * d)
             elif ty == GGUFType.Q2_0:  # d * (lo + 2*hi - sum)
                 d = rows[r, b, 0:2].copy().view(np.float16).astype(f32)[0]
@@ -127,7 +144,8 @@ def ref_matvec(ty, blocks, deq, k, m, x):
 
 
 def main():
-    for ty in (GGUFType.Q8_0, GGUFType.Q4_K, GGUFType.IQ2_XXS, GGUFType.Q2_0):
+    for ty in (GGUFType.Q8_0, GGUFType.Q4_K, GGUFType.IQ2_XXS, GGUFType.Q2_0, GGUFType.Q4_0, GGUFType.IQ4_NL,
+               GGUFType.Q5_K, GGUFType.Q6_K):
         rng = np.random.default_rng(1000 + int(ty))
         per = block_elems(ty)
         k, m = 4 * 256, 6

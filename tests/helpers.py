@@ -8,6 +8,8 @@ from chatokf_b200.gguf_types import GGUFType, block_elems
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 ALL_TYPES = [GGUFType.Q8_0, GGUFType.Q4_K, GGUFType.IQ2_XXS, GGUFType.Q2_0]
+# the rest of the decoder table: same entry points, plain kernels
+MORE_TYPES = [GGUFType.Q4_0, GGUFType.IQ4_NL, GGUFType.Q5_K, GGUFType.Q6_K]
 
 
 def golden(ty):

@@ -13,7 +13,7 @@ import oracle
 from chatokf_b200 import synth
 from chatokf_b200.enc import BF16, F16, F32, CudaEnc, GGUFTensor, OkfError, QB
 from chatokf_b200.gguf_types import GGUFType, block_bytes, block_elems, row_byte_count
-from helpers import ALL_TYPES, golden, lcg_fill, make_weights, rel_err
+from helpers import ALL_TYPES, MORE_TYPES, golden, lcg_fill, make_weights, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -37,7 +37,7 @@ def dev(a, dtype=None):
 
 # ---- dequant: bit-exact ------------------------------------------------------
 
-@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("ty", ALL_TYPES + MORE_TYPES)
 def test_dequant_golden_bits(ctx, ty):
     g = golden(ty)
     enc = CudaEnc(ctx)
@@ -50,17 +50,17 @@ def test_dequant_golden_bits(ctx, ty):
         assert np.array_equal(out.cpu().numpy().view(np.uint32), bits)
 
 
-@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("ty", ALL_TYPES + MORE_TYPES)
 def test_dequant_random_blocks_bit_exact(ctx, ty):
     rng = np.random.default_rng(11)
-    nblk = 100_000 if ty != GGUFType.Q8_0 else 400_000
+    nblk = 100_000 if block_elems(ty) > 32 else 400_000
     blocks = synth.random_blocks(ty, nblk, rng)
     want = oracle.dequant(ty, blocks)
     got = QB(ctx).dequant(GGUFTensor("t", (nblk * block_elems(ty), 1), ty), ctx.upload(blocks), 0, want.size)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("ty", ALL_TYPES)
+@pytest.mark.parametrize("ty", ALL_TYPES + MORE_TYPES)
 def test_dequant_row_slice(ctx, ty):
     """dequantRow at a row offset inside a larger buffer (embedding-row read)."""
     k, m = 1024, 7
@@ -600,3 +600,34 @@ def test_host_twin_inside_a_parallel_region_returns_a_finished_result(ctx):
         assert np.isfinite(got).all()
     assert rel_err(got, oracle.matvec(ty, blocks, k, m, x)) <= GEMV_TIGHT
     assert ctx.fallbacks == fallbacks  # the tensor-core matvec took it
+
+
+# ---- the rest of the decoder table (Q4_0, IQ4_NL, Q5_K, Q6_K): same entry points, plain kernels ----
+
+@pytest.mark.parametrize("ty", MORE_TYPES)
+def test_more_types_golden_matvec_and_matmul(ctx, ty):
+    """The types gemma trunks and mixed K-quant files add (Blocks.decoder,
+    LLM/Quantize/Blocks.swift:10-29; GQ.matvec's q4_0 / iq4_nl arms,
+    LLM/Gemma/Gemma4Quant.swift:93-114): the committed fixture, then 1, 4 and 33 columns
+    against the oracle.  They run on the warp-per-row / fp32-tile kernels with exact
+    decode, so the matvec bound applies at every width, and each call is counted as a
+    fallback."""
+    g = golden(ty)
+    k, m = int(g["k"]), int(g["m"])
+    got = QB(ctx).matvec(GGUFTensor("w", (k, m), ty), ctx.upload(g["blocks"]), g["x"])
+    assert rel_err(got, g["matvec"]) <= GEMV_TIGHT
+    enc = CudaEnc(ctx)
+    for k, m, n in [(2048, 200, 1), (1024, 131, 4), (1024, 131, 33)]:
+        blocks = make_weights(ty, m, k, seed=k + n)
+        X = np.stack([lcg_fill(k, 500 + c) for c in range(n)])
+        for xdt in (F32, F16):
+            Xd = dev(X, TORCH_DT[xdt])
+            before = ctx.fallbacks
+            out = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
+            enc.gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
+            torch.cuda.synchronize()
+            assert ctx.fallbacks == before + 1
+            o = out.cpu().numpy()
+            assert np.isnan(o[n * m:]).all()
+            ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
+            assert rel_err(o[:n * m].reshape(n, m), ref) <= GEMV_TIGHT, (GGUFType(ty).name, k, m, n, xdt)

@@ -19,7 +19,9 @@ def test_q8_0_follows_the_stated_recipe():
     assert np.array_equal(q, np.clip(np.rint(w.reshape(-1, 32) / d[:, None]), -128, 127).astype(np.int8))
 
 
-@pytest.mark.parametrize("ty,tol", [(GGUFType.Q8_0, 0.01), (GGUFType.Q4_K, 0.12), (GGUFType.IQ2_XXS, 0.45)])
+@pytest.mark.parametrize("ty,tol", [(GGUFType.Q8_0, 0.01), (GGUFType.Q4_K, 0.12), (GGUFType.IQ2_XXS, 0.45),
+                                    (GGUFType.Q4_0, 0.15), (GGUFType.IQ4_NL, 0.12), (GGUFType.Q5_K, 0.06),
+                                    (GGUFType.Q6_K, 0.04)])
 def test_fitted_blocks_approximate_the_weights(ty, tol):
     rng = np.random.default_rng(1)
     w = rng.normal(0, 0.02, size=(4, 1024)).astype(np.float32)
