@@ -15,6 +15,7 @@ OKF_OK = 0
 STATUS = {
     0: "OKF_OK", -1: "OKF_E_ARG", -2: "OKF_E_TYPE", -3: "OKF_E_SHAPE", -4: "OKF_E_RANGE",
     -5: "OKF_E_ALIGN", -6: "OKF_E_CUDA", -7: "OKF_E_NOMEM", -8: "OKF_E_INJECTED", -9: "OKF_E_LIMIT",
+    -10: "OKF_E_FORMAT", -11: "OKF_E_IO",
 }
 
 # every symbol include/okf_cuda.h declares: name -> (restype, argtypes)
@@ -77,6 +78,33 @@ class SrqSide(ctypes.Structure):
     """okf_srq_side"""
     _fields_ = [("scale", ctypes.c_float), ("lo", ctypes.c_float), ("hi", ctypes.c_float)]
 
+
+class GGUFTensorInfo(ctypes.Structure):
+    """okf_gguf_tensor"""
+    _fields_ = [("name", ctypes.c_char_p), ("n_dims", _u32), ("dims", _u64 * 4), ("type", ctypes.c_int32),
+                ("offset", _u64), ("bytes", _u64), ("host", _vp)]
+
+
+_cs, _pu64 = ctypes.c_char_p, ctypes.POINTER(_u64)
+SIGNATURES.update({
+    "okf_gguf_open": (_ci, [_cs, _pp]),
+    "okf_gguf_close": (None, [_vp]),
+    "okf_gguf_version": (_u32, [_vp]),
+    "okf_gguf_tensor_count": (_u64, [_vp]),
+    "okf_gguf_tensor_at": (_ci, [_vp, _u64, ctypes.POINTER(GGUFTensorInfo)]),
+    "okf_gguf_find": (_ci, [_vp, _cs, ctypes.POINTER(GGUFTensorInfo)]),
+    "okf_gguf_data_offset": (_u64, [_vp]),
+    "okf_gguf_data_bytes": (_u64, [_vp]),
+    "okf_gguf_meta_count": (_u64, [_vp]),
+    "okf_gguf_meta_key": (_cs, [_vp, _u64]),
+    "okf_gguf_meta_kind": (_ci, [_vp, _cs]),
+    "okf_gguf_meta_int": (_ci, [_vp, _cs, ctypes.POINTER(ctypes.c_int64)]),
+    "okf_gguf_meta_double": (_ci, [_vp, _cs, ctypes.POINTER(ctypes.c_double)]),
+    "okf_gguf_meta_string": (_ci, [_vp, _cs, _pp, _pu64]),
+    "okf_gguf_meta_array": (_ci, [_vp, _cs, _pu64, _pp, _pp]),
+    "okf_gguf_meta_string_at": (_ci, [_vp, _cs, _u64, _pp, _pu64]),
+    "okf_gguf_upload": (_ci, [_vp, _vp, _pp]),
+})
 
 _f = ctypes.c_float
 SIGNATURES.update({

@@ -154,6 +154,8 @@ const char *okf_strerror(int status) {
     case OKF_E_NOMEM: return "out of memory";
     case OKF_E_INJECTED: return "staged fault fired (okf_fault_inject)";
     case OKF_E_LIMIT: return "size beyond a fixed maximum";
+    case OKF_E_FORMAT: return "not a GGUF file, or a truncated or malformed one";
+    case OKF_E_IO: return "file could not be opened or mapped";
     default: return "unknown status";
     }
 }

@@ -66,7 +66,9 @@ typedef enum okf_status {
     OKF_E_CUDA = -6,     /* a CUDA call failed; see okf_last_cuda_error       */
     OKF_E_NOMEM = -7,    /* host or device allocation failed                  */
     OKF_E_INJECTED = -8, /* a staged fault from okf_fault_inject fired        */
-    OKF_E_LIMIT = -9     /* a size exceeds a documented fixed maximum         */
+    OKF_E_LIMIT = -9,    /* a size exceeds a documented fixed maximum         */
+    OKF_E_FORMAT = -10,  /* not a GGUF file, or a truncated / malformed one   */
+    OKF_E_IO = -11       /* the file could not be opened or mapped            */
 } okf_status;
 
 typedef struct okf_ctx okf_ctx;         /* replaces MetalContext (Base/MetalContext.swift:58-80) */
@@ -236,6 +238,49 @@ OKF_API int okf_gemm_noalloc(okf_ctx *ctx, int type, const okf_weights *w, uint6
  * (Gemma/Gemma4Quant.swift:320-364, Base/Quant.swift:73-76). */
 OKF_API int okf_dequant(okf_ctx *ctx, int type, const okf_weights *w, uint64_t woff, uint64_t count,
                 float *out, okf_stream stream);
+
+/* ---- GGUF files ---------------------------------------------------------------------
+ * Replaces GGUF.init (Base/GGUF.swift:92-158): the file is mapped read-only and parsed
+ * once; tensors keep the file's order.  dims[0] is the fastest axis (K of a weight
+ * matrix), dims[1] its rows (M).  `offset` counts from the start of the data region,
+ * which okf_gguf_upload copies to the GPU in one piece (the zero-copy windows of
+ * Base/MetalContext.swift:114-185 become one device allocation), so a tensor's offset
+ * is the woff of okf_gemv / okf_gemm / okf_dequant / okf_embed_batch.  An id the
+ * reference's GGUFType does not know is OKF_E_TYPE, as it is a parse error there. */
+typedef struct okf_gguf okf_gguf;
+typedef struct okf_gguf_tensor {
+    const char *name;   /* owned by the okf_gguf */
+    uint32_t n_dims;
+    uint64_t dims[4];   /* unused axes are 1 */
+    int32_t type;       /* ggml type id */
+    uint64_t offset;    /* bytes from the start of the data region */
+    uint64_t bytes;     /* GGUF.rowByteCount(type, element count) */
+    const void *host;   /* the tensor's bytes in the mapping */
+} okf_gguf_tensor;
+OKF_API int okf_gguf_open(const char *path, okf_gguf **out);
+OKF_API void okf_gguf_close(okf_gguf *g);
+OKF_API uint32_t okf_gguf_version(const okf_gguf *g);
+OKF_API uint64_t okf_gguf_tensor_count(const okf_gguf *g);
+OKF_API int okf_gguf_tensor_at(const okf_gguf *g, uint64_t index, okf_gguf_tensor *out);
+OKF_API int okf_gguf_find(const okf_gguf *g, const char *name, okf_gguf_tensor *out); /* OKF_E_RANGE: no such tensor */
+OKF_API uint64_t okf_gguf_data_offset(const okf_gguf *g); /* where the data region starts in the file */
+OKF_API uint64_t okf_gguf_data_bytes(const okf_gguf *g);
+/* Metadata (GGUFValue, Base/GGUF.swift:15-23).  kind: 0 absent, 1 integer, 2 floating
+ * point, 3 string, 4 bool, 5 integer array, 6 floating-point array, 7 string table.
+ * Strings point into the mapping and are NOT terminated: use the length.  A missing key is
+ * OKF_E_RANGE, a key of another kind OKF_E_TYPE (integers read as doubles too). */
+OKF_API uint64_t okf_gguf_meta_count(const okf_gguf *g);
+OKF_API const char *okf_gguf_meta_key(const okf_gguf *g, uint64_t index);
+OKF_API int okf_gguf_meta_kind(const okf_gguf *g, const char *key);
+OKF_API int okf_gguf_meta_int(const okf_gguf *g, const char *key, int64_t *out);
+OKF_API int okf_gguf_meta_double(const okf_gguf *g, const char *key, double *out);
+OKF_API int okf_gguf_meta_string(const okf_gguf *g, const char *key, const char **out, uint64_t *len);
+OKF_API int okf_gguf_meta_array(const okf_gguf *g, const char *key, uint64_t *count, const int64_t **ints,
+                                const double **doubles);
+OKF_API int okf_gguf_meta_string_at(const okf_gguf *g, const char *key, uint64_t index, const char **out,
+                                    uint64_t *len);
+/* The whole data region into one device allocation (okf_weights_upload of it). */
+OKF_API int okf_gguf_upload(okf_ctx *ctx, const okf_gguf *g, okf_weights **out);
 
 /* ---- the linears' neighbours in the engines' command streams ---------------------
  * Small memory-bound operators that read or write the same activations as the
