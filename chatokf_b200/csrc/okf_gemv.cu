@@ -59,20 +59,31 @@ struct GemvLayout {
     uint32_t smem_bytes;
 };
 
-constexpr uint32_t kBarBytes = 384;   // barriers and the abort flag, then 128 bytes of zeros at kZeroOff
+constexpr uint32_t kBarBytes = 512;   // barriers and the abort flag, then 256 bytes of zeros at kZeroOff
 constexpr uint32_t kZeroOff = 256;    // what the lanes that feed nothing into an MMA read instead of x
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kConsumers = kGemvWarps * 32;
-// SEP x panel: a unit of a byte column is its 256 bytes in k order, except that
-// in quarters 2 and 3 neighbouring 16-byte pieces are swapped; with the second
-// byte column 32 (mod 128) bytes after the first, the eight lanes of a load that
-// carry data (4 quarters x 2 byte columns) touch eight different bank groups.
+// WIDE x panel: a unit of a byte column is its 256 bytes in k order, except that in
+// quarters 2 and 3 neighbouring 16-byte pieces are swapped; with the second byte column
+// 32 (mod 128) bytes after the first, the lanes of a load that carry data touch different
+// bank groups.
 constexpr uint32_t kXqUnit = 256;
 constexpr float kXqMax = 32512.f;  // 127 * 256: hi stays a signed byte after rounding
+// SEP x panel: per byte column and unit, four quarters of 80 bytes: 64 bytes of x in k
+// order, then (first byte column only) the quarter's record {scale, scale * sum of x over
+// its first 32-wide block, over its second, -}.  One address register reaches a
+// quarter's x and its record with immediate offsets.  80-byte quarters put the four
+// quarters of a 16-byte access on different bank groups (0, 80, 32, 112 mod 128) and the
+// second byte column, 64 (mod 128) bytes after the first, on the other four.
+constexpr uint32_t kSepQuarter = 80, kSepUnit = 4 * kSepQuarter;
 
 __host__ __device__ inline uint32_t xq_col_stride(uint32_t units) {
     const uint32_t raw = units * kXqUnit;
     return raw + ((32u + 128u - raw % 128u) % 128u);
+}
+__host__ __device__ inline uint32_t sep_col_stride(uint32_t units) {
+    const uint32_t raw = units * kSepUnit;
+    return raw + ((64u + 128u - raw % 128u) % 128u);
 }
 __host__ __device__ inline uint32_t xq_piece_offset(uint32_t c, uint32_t piece) {
     return c * 64 + ((piece ^ (c >> 1)) & 3u) * 16;
@@ -223,7 +234,8 @@ struct SepConst {
     uint32_t sel, m1, m2;   // Q4_K: how to pick this thread's 6-bit scales and mins out of the 12 bytes
     bool low;               // Q4_K: sub-blocks 0..3 (plain 6-bit fields) or 4..7 (split fields)
     uint32_t tab_lane;      // IQ2_XXS: shared address of this lane's copy of codebook entry 0
-    uint32_t tab_stride;    // IQ2_XXS: bytes between codebook entries (copies of one entry lie side by side)
+    uint32_t sgn_lane;      // IQ2_XXS: the same for the table of sign masks that follows the codebook
+    uint32_t tab_stride;    // IQ2_XXS: bytes between table entries (copies of one entry lie side by side)
 };
 template <int TY>
 __device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_t tab, uint32_t tab_copies) {
@@ -243,6 +255,7 @@ __device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_
         k.qoff = 2 + 16 * c;
         k.tab_lane = tab + (lane & (tab_copies - 1)) * 8;
         k.tab_stride = tab_copies * 8;
+        k.sgn_lane = k.tab_lane + 256 * k.tab_stride;
     }
     return k;
 }
@@ -260,8 +273,9 @@ __device__ __forceinline__ void iq2_sign_bytes(uint32_t idx7, uint32_t &lo, uint
 
 // ua / ub: shared addresses of the unit in rows g and g + 8.  xf: this thread's 64
 // bytes of x (its quarter of the unit, the byte column its MMA column stands for; zeros
-// in the lanes that feed nothing).  xi: {scale of x in this unit, integer sum of x over
-// the first 32-wide block of the quarter, over the second, -}.  acc: rows g and g + 8.
+// in the lanes that feed nothing).  xi: {scale of x in this unit, scale * sum of x over
+// the first 32-wide block of the quarter, over the second, -} as float bits.
+// acc: rows g and g + 8.
 template <int TY>
 __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepConst &K, const uint32_t (&xf)[16],
                                          const uint4 &xi, float (&acc)[2]) {
@@ -291,17 +305,20 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
         const uint32_t pa = prmt(ha.y, hb.y, K.sel), pb = prmt(ha.z, hb.z, K.sel), pe = prmt(ha.w, hb.w, K.sel);
         const uint32_t sc = ((K.low ? pa : pe) & K.m1) | ((pa >> 2) & K.m2);
         const uint32_t mn = ((K.low ? pb : (pe >> 4)) & K.m1) | ((pb >> 2) & K.m2);
-        // Integer all the way: |sum of 32 nibbles x 16-bit x| < 2^24, times a 6-bit scale
-        // < 2^30, two of them < 2^31.
-        const int jla = lo[0] * 256 + lo[1], jha = (hi[0] * 256 + hi[1]) >> 4;
-        const int jlb = lo[2] * 256 + lo[3], jhb = (hi[2] * 256 + hi[3]) >> 4;
-        const int sa = ubyte(sc, 0) * jla + ubyte(sc, 1) * jha, sb = ubyte(sc, 2) * jlb + ubyte(sc, 3) * jhb;
-        const int x0 = (int)xi.y, x1 = (int)xi.z;
-        const int ma = ubyte(mn, 0) * x0 + ubyte(mn, 1) * x1, mb = ubyte(mn, 2) * x0 + ubyte(mn, 3) * x1;
+        // From here on floating point: integer instructions run at half the rate of fp32 ones
+        // on this part, and the masks above have used up the integer budget.  A scale byte
+        // becomes a float with one byte permute and one subtraction.  The high-nibble sums
+        // carry a factor 16 that goes into x's scale.
+        const float xs16 = xs * 0.0625f;
+        const float la = join_hi_lo(lo[0], lo[1]), ha_ = join_hi_lo(hi[0], hi[1]);
+        const float lb = join_hi_lo(lo[2], lo[3]), hb_ = join_hi_lo(hi[2], hi[3]);
+        const float x0 = __uint_as_float(xi.y), x1 = __uint_as_float(xi.z);  // scale * sum of x per block
         const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&ha.x));
         const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&hb.x));
-        acc[0] += xs * (fa.x * (float)sa - fa.y * (float)ma);
-        acc[1] += xs * (fb.x * (float)sb - fb.y * (float)mb);
+        acc[0] += fa.x * (byte_to_f32(sc, 0) * (xs * la) + byte_to_f32(sc, 1) * (xs16 * ha_)) -
+                  fa.y * (byte_to_f32(mn, 0) * x0 + byte_to_f32(mn, 1) * x1);
+        acc[1] += fb.x * (byte_to_f32(sc, 2) * (xs * lb) + byte_to_f32(sc, 3) * (xs16 * hb_)) -
+                  fb.y * (byte_to_f32(mn, 2) * x0 + byte_to_f32(mn, 3) * x1);
     } else if constexpr (TY == T_Q8_0) {
         // eight blocks {f16 d; i8 q[32]} (LLM/Gemma/Gemma4Quant.swift:51-69); thread c
         // takes blocks 2c and 2c+1: {d0, q0[32], d1, q1[32]} = 17 words (units start on
@@ -357,17 +374,19 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
                 for (int e = 0; e < 4; e++) t[e] = t[e] + d[e] * (64 >> (2 * s));
             }
         }
-        const float xsum = (float)((int)xi.y + (int)xi.z);
-        acc[0] += xs * da * (0.015625f * join_hi_lo(t[0], t[1]) - xsum);
-        acc[1] += xs * db * (0.015625f * join_hi_lo(t[2], t[3]) - xsum);
+        const float xsum = __uint_as_float(xi.y) + __uint_as_float(xi.z);  // scale * sum of x over the quarter
+        acc[0] += da * (xs * 0.015625f * join_hi_lo(t[0], t[1]) - xsum);
+        acc[1] += db * (xs * 0.015625f * join_hi_lo(t[2], t[3]) - xsum);
     } else {
         // IQ2_XXS {f16 d; 8 x (u32 a0: four codebook indices, u32 a1: four 7-bit sign
         // indices + 4-bit scale)} (LLM/Quantize/IQ2XXS.swift:34-53).  Thread c takes
         // sub-blocks 2c and 2c+1.  A codebook entry is eight magnitude bytes = the two
-        // A registers of one row.  Signs: XOR with the sign's byte mask turns a magnitude
-        // m into the signed byte -(m + 1); a second MMA on the masks themselves (255 per
-        // negative weight) gives 255 x the sum of x over the negative weights, which puts
-        // the missing 1 back: sum(sign * m * x) = D1 + D2 / 255.
+        // A registers of one row; the byte masks of a sign index (0xFF = negative) come from
+        // a second table (integer instructions are the scarce resource here, shared-memory
+        // look-ups without bank conflicts are not).  Signs: XOR with the mask turns a
+        // magnitude m into the signed byte -(m + 1); a second MMA on the masks themselves
+        // (255 per negative weight) gives 255 x the sum of x over the negative weights, which
+        // puts the missing 1 back: sum(sign * m * x) = D1 + D2 / 255.
         uint32_t wa[4], wb[4];
         lds_a2<4>(ua + K.qoff, wa);
         lds_a2<4>(ub + K.qoff, wb);
@@ -381,16 +400,15 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
             for (int l = 0; l < 4; l++) {
                 const uint2 ea = lds64(K.tab_lane + prmt(a0a, 0u, 0x4440u + l) * K.tab_stride);
                 const uint2 eb = lds64(K.tab_lane + prmt(a0b, 0u, 0x4440u + l) * K.tab_stride);
-                uint32_t mal, mah, mbl, mbh;
-                iq2_sign_bytes((a1a >> (7 * l)) & 127u, mal, mah);
-                iq2_sign_bytes((a1b >> (7 * l)) & 127u, mbl, mbh);
+                const uint2 ma = lds64(K.sgn_lane + ((a1a >> (7 * l)) & 127u) * K.tab_stride);
+                const uint2 mb = lds64(K.sgn_lane + ((a1b >> (7 * l)) & 127u) * K.tab_stride);
                 const uint32_t x0 = xf[8 * sb + 2 * l], x1 = xf[8 * sb + 2 * l + 1];
                 if (l == 0) {
-                    imma0<true>(d1, ea.x ^ mal, eb.x ^ mbl, ea.y ^ mah, eb.y ^ mbh, x0, x1);
-                    imma0<false>(d2, mal, mbl, mah, mbh, x0, x1);
+                    imma0<true>(d1, ea.x ^ ma.x, eb.x ^ mb.x, ea.y ^ ma.y, eb.y ^ mb.y, x0, x1);
+                    imma0<false>(d2, ma.x, mb.x, ma.y, mb.y, x0, x1);
                 } else {
-                    imma<true>(d1, ea.x ^ mal, eb.x ^ mbl, ea.y ^ mah, eb.y ^ mbh, x0, x1);
-                    imma<false>(d2, mal, mbl, mah, mbh, x0, x1);
+                    imma<true>(d1, ea.x ^ ma.x, eb.x ^ mb.x, ea.y ^ ma.y, eb.y ^ mb.y, x0, x1);
+                    imma<false>(d2, ma.x, mb.x, ma.y, mb.y, x0, x1);
                 }
             }
             sum[sb][0] = fmaf(join_hi_lo(d2[0], d2[1]), 1.f / 255.f, join_hi_lo(d1[0], d1[1]));
@@ -600,22 +618,21 @@ __device__ __forceinline__ void quantize16(const XRaw<XDT> &raw, int (&q)[16], f
 // above infinity, so a NaN anywhere in the unit comes out on top and is seen).
 // Rounding: v * inv + (1.5 * 2^23 + 128) lands where the float's low mantissa bits are
 // the integer q + 128 = 256 * hi + (lo + 128): hi is byte 1, lo is byte 0 with its top
-// bit flipped.  Byte order inside a unit: k order, the 16-byte pieces of quarters 2 and
-// 3 swapped in pairs (Q2_0: inside each 16, byte 4s + b holds k = s + 4b, the order the
-// masked code words come in).
-// info[unit * 4 + quarter] = {scale, integer sum of x over the quarter's first 32-wide
-// block, over its second, -}.
+// bit flipped.  Byte order inside a quarter: k order (Q2_0: inside each 16, byte 4s + b
+// holds k = s + 4b, the order the masked code words come in).  The quarter's record
+// {scale, scale * sum of x over its first 32-wide block, over its second} follows its 64
+// bytes in the first byte column.
 template <int XDT> struct XRaw8 { uint4 v[XDT == DT_F32 ? 2 : 1]; };
 
 template <int TY, int XDT>
-__device__ __forceinline__ void stage_x_bytes(uint32_t xs32, uint32_t es, uint32_t info32, const void *x,
-                                              uint32_t u_first, uint32_t nu, uint32_t tid) {
+__device__ __forceinline__ void stage_x_bytes(uint32_t xs32, uint32_t es, const void *x, uint32_t u_first, uint32_t nu,
+                                              uint32_t tid) {
     const uint32_t items = nu * 32;
     constexpr uint32_t kFlight = 4;  // items a thread has in flight: the loads go out first
     constexpr uint32_t kMagicBits = 0x4B400080u;  // 1.5 * 2^23 + 128 as a float
     const uint32_t e8 = tid & 31;  // this lane's item inside its unit, the same in every pass
     const uint32_t c = e8 >> 3;
-    const uint32_t piece_off = c * 64 + ((((e8 >> 1) & 3) ^ (c >> 1)) & 3) * 16;
+    const uint32_t item_off = c * kSepQuarter + (e8 & 7) * 8;  // 8 bytes of the quarter's 64
     for (uint32_t base = tid; base < items; base += kFlight * kConsumers) {
         XRaw8<XDT> raw[kFlight];
 #pragma unroll
@@ -670,25 +687,26 @@ __device__ __forceinline__ void stage_x_bytes(uint32_t xs32, uint32_t es, uint32
             qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
             qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
             const uint32_t u = i >> 5;
-            const uint32_t dst = xs32 + u * kXqUnit + piece_off;
+            const uint32_t dst = xs32 + u * kSepUnit + item_off;
             if constexpr (TY == T_Q2_0) {
                 // this item is half (e8 & 1) of a 16: bytes 2h, 2h + 1 of each of its four words
+                const uint32_t at16 = dst - (e8 & 1) * 8;
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
-                    const uint32_t at = dst + 4 * w + 2 * (e8 & 1);
+                    const uint32_t at = at16 + 4 * w + 2 * (e8 & 1);
                     sts16(at, prmt(t[w], t[w + 4], 0x0051u) & 0xFFFFu);
                     sts16(at + es, (prmt(t[w], t[w + 4], 0x0040u) & 0xFFFFu) ^ 0x8080u);
                 }
             } else {
-                const uint32_t at = dst + 8 * (e8 & 1);
-                sts64(at, prmt(prmt(t[0], t[1], 0x0051u), prmt(t[2], t[3], 0x0051u), 0x5410u),
+                sts64(dst, prmt(prmt(t[0], t[1], 0x0051u), prmt(t[2], t[3], 0x0051u), 0x5410u),
                       prmt(prmt(t[4], t[5], 0x0051u), prmt(t[6], t[7], 0x0051u), 0x5410u));
-                sts64(at + es, prmt(prmt(t[0], t[1], 0x0040u), prmt(t[2], t[3], 0x0040u), 0x5410u) ^ 0x80808080u,
+                sts64(dst + es, prmt(prmt(t[0], t[1], 0x0040u), prmt(t[2], t[3], 0x0040u), 0x5410u) ^ 0x80808080u,
                       prmt(prmt(t[4], t[5], 0x0040u), prmt(t[6], t[7], 0x0040u), 0x5410u) ^ 0x80808080u);
             }
-            const uint32_t rec = info32 + (u * 4 + c) * 16;
+            // the quarter's record, behind its 64 bytes in the first byte column
+            const uint32_t rec = xs32 + u * kSepUnit + c * kSepQuarter + 64;
             if ((e8 & 7) == 0) sts32(rec, __float_as_uint(scale));
-            if ((e8 & 3) == 0) sts32(rec + 4 + ((e8 >> 2) & 1) * 4, (uint32_t)qsum);
+            if ((e8 & 3) == 0) sts32(rec + 4 + ((e8 >> 2) & 1) * 4, __float_as_uint(scale * (float)qsum));
         }
     }
 }
@@ -780,8 +798,11 @@ struct RingPos {
     }
 };
 
+#ifndef OKF_GEMV_MINB
+#define OKF_GEMV_MINB 2
+#endif
 template <int TY, int XDT, bool SEP>
-__global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, GemvLayout L, GemvGather G) {
+__global__ void __launch_bounds__(kGemvThreadsMax, OKF_GEMV_MINB) gemv_kernel(GemvArgs p, GemvLayout L, GemvGather G) {
     constexpr uint32_t UB = UnitGeom<TY>::bytes;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -808,7 +829,7 @@ __global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, Ge
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (threadIdx.x < 32) reinterpret_cast<uint32_t *>(smem + kZeroOff)[threadIdx.x] = 0u;
+    if (threadIdx.x < 64) reinterpret_cast<uint32_t *>(smem + kZeroOff)[threadIdx.x] = 0u;
     if constexpr (TY == T_IQ2_XXS) {
         // The codebook, 256 entries of eight magnitude bytes, every entry `tab_copies`
         // times side by side: a lane reads copy (lane mod copies), so with 16 copies the
@@ -816,6 +837,13 @@ __global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, Ge
         uint64_t *tw = reinterpret_cast<uint64_t *>(smem + L.tab_off);
         const uint32_t sh = 31 - __clz(L.tab_copies);
         for (uint32_t i = threadIdx.x; i < 256 * L.tab_copies; i += blockDim.x) tw[i] = g_iq2xxs_grid[i >> sh];
+        // and behind it the byte masks of the 128 sign indices, laid out the same way
+        uint2 *sw = reinterpret_cast<uint2 *>(tw + 256 * L.tab_copies);
+        for (uint32_t i = threadIdx.x; i < 128 * L.tab_copies; i += blockDim.x) {
+            uint2 m;
+            iq2_sign_bytes(i >> sh, m.x, m.y);
+            sw[i] = m;
+        }
     }
     __syncthreads();
 
@@ -844,7 +872,7 @@ __global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, Ge
                     tn = min(min(L.tps, gb + gn - tl), sg.tile1 - (t0 + tl));  // a step stays inside one matrix
                     for (uint32_t half = 0; half < spt; half++, issued++) {
                         if (rp.use > 0 &&
-                            !mbar_wait(&empty[rp.s], (rp.use - 1) & 1, abort_flag, p.status, kStatusEmptyTimeout)) {
+                            !mbar_wait_relaxed(&empty[rp.s], (rp.use - 1) & 1, abort_flag, p.status, kStatusEmptyTimeout)) {
                             // giving up: let the copies already issued land before the CTA goes away
                             const uint32_t first = issued > L.nstage ? issued - L.nstage : 0;
                             for (uint32_t d = first; d < issued; d++) {
@@ -913,14 +941,16 @@ __global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, Ge
     const uint8_t *xs_mine = xs + (SEP ? (g & 1) : g) * L.es + c * 64;
     const uint32_t xs_ustride = kXqUnit;
     const uint32_t xq_swap = (c >> 1) * 16;
-    // the same in shared-window addresses for the one-column path; lanes that feed nothing
-    // read the page of zeros (stride 0) instead of predicating every load
+    // The same in shared-window addresses for the one-column path.  Lanes that feed nothing
+    // read zeros (stride 0) instead of predicating every load; their zeros sit on a bank
+    // group that the two lanes carrying data in the same 8-lane phase do not touch.
     const SepConst KC = sep_const<TY>(c, lane, smem32 + L.tab_off, L.tab_copies);
     const uint32_t stages32 = smem32 + kBarBytes;
-    const uint32_t xbase32 = SEP && x_active ? smem32 + L.xs_off + (g & 1) * L.es + c * 64 : smem32 + kZeroOff;
-    const uint32_t xs_s = xbase32 + xq_swap, xs_t = xbase32 + 16 - xq_swap;
-    const uint32_t xstride32 = SEP && x_active ? kXqUnit : 0u;
-    const uint32_t info_c = smem32 + L.info_off + c * 16;
+    const uint32_t xbase32 = SEP && x_active ? smem32 + L.xs_off + (g & 1) * L.es + c * kSepQuarter
+                                             : smem32 + kZeroOff + ((5 * (g >> 1) + 1) & 7) * 16;
+    const uint32_t xstride32 = SEP && x_active ? kSepUnit : 0u;
+    const uint32_t rec32 = smem32 + L.xs_off + c * kSepQuarter + 64;  // this quarter's record of unit 0
+    const uint32_t red32 = smem32 + L.red_off + (warp * 16 + g + 8 * (c & 1)) * 4;  // this thread's slot of tile 0
     // WIDE: this lane's copy of the IQ2_XXS codebook
     const uint2 *tab = reinterpret_cast<const uint2 *>(smem + L.tab_off) + (lane & (L.tab_copies - 1));
     RingPos rp;
@@ -947,7 +977,7 @@ __global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, Ge
             if (gb == 0 || L.panel < p.nchunk) {
                 // the previous panel is still being read until every warp gets here
                 if (gb > 0 || j0 > 0) consumer_sync();
-                if constexpr (SEP) stage_x_bytes<TY, XDT>(smem32 + L.xs_off, L.es, smem32 + L.info_off, p.x, pu0, pnu, tid);
+                if constexpr (SEP) stage_x_bytes<TY, XDT>(smem32 + L.xs_off, L.es, p.x, pu0, pnu, tid);
                 else stage_x_wide<TY, XDT>(xs, reinterpret_cast<float *>(info), L, p.x, p.k, pu0, pnu, tid);
             }
             consumer_sync();
@@ -990,36 +1020,53 @@ __global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, Ge
                     rot = (rot + total) % kGemvWarps;
                     uint32_t ti = 0, u = v;
                     while (u >= nu && ti < tn) { u -= nu; ti++; }
+                    if constexpr (SEP) {
+                        // Integer instructions run at half the rate of the others on this part and
+                        // the unit bodies are full of them, so the walk over this warp's units
+                        // keeps a handful of addresses and moves them by constants.
+                        uint32_t wa = stages32 + (uint32_t)(ra - stages) + ti * tile_bytes + (ubase + u) * UB;  // row g
+                        const uint32_t wdelta = (uint32_t)(rb - ra);                                            // to row g + 8
+                        uint32_t xa = xbase32 + (pu + u) * xstride32;
+                        uint32_t ia = rec32 + (pu + u) * kSepUnit;
+                        uint32_t da = red32 + (tl - gb + ti) * (kGemvWarps * 16 * 4);
+                        float acc[2] = {0.f, 0.f};
+                        while (v < total) {
+                            const uint4 q0 = lds128(xa), q1 = lds128(xa + 16), q2 = lds128(xa + 32), q3 = lds128(xa + 48);
+                            const uint32_t xf[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
+                                                     q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+                            const uint4 xi = lds128(ia);
+                            unit_sep<TY>(wa, wa + wdelta, KC, xf, xi, acc);
+                            v += kGemvWarps;
+                            u += kGemvWarps;
+                            wa += kGemvWarps * UB;
+                            xa += kGemvWarps * xstride32;
+                            ia += kGemvWarps * kSepUnit;
+                            if (u >= nu || v >= total) {
+                                // this warp is through with the tile: each thread of a quad covered
+                                // another quarter; add them up and put the sums into the warp's slot
+#pragma unroll
+                                for (int e = 0; e < 2; e++) {
+                                    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+                                    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+                                }
+                                if (c < 2) sts32(da, __float_as_uint(__uint_as_float(lds32(da)) + (c ? acc[1] : acc[0])));
+                                acc[0] = acc[1] = 0.f;
+                                while (u >= nu) {  // on to the next tile (more than one when a tile has few units)
+                                    u -= nu;
+                                    wa += tile_bytes - nu * UB;
+                                    xa -= nu * xstride32;
+                                    ia -= nu * kSepUnit;
+                                    da += kGemvWarps * 16 * 4;
+                                }
+                            }
+                        }
+                    } else {
                     while (v < total) {
                         const uint32_t cur = ti;
                         const uint8_t *ta = ra + (size_t)cur * tile_bytes, *tb = rb + (size_t)cur * tile_bytes;
                         // this warp's own slot of the tile's partial sums
                         float *dst = red + ((size_t)(tl - gb + cur) * kGemvWarps + warp) * 16 * L.nc;
-                        if constexpr (SEP) {
-                            float acc[2] = {0.f, 0.f};
-                            const uint32_t ta32 = stages32 + (uint32_t)(ta - stages), tb32 = stages32 + (uint32_t)(tb - stages);
-                            do {
-                                // quarters 2 and 3 keep their 16-byte pieces swapped in pairs
-                                const uint32_t xo = (pu + u) * xstride32;
-                                const uint4 q0 = lds128(xs_s + xo), q1 = lds128(xs_t + xo);
-                                const uint4 q2 = lds128(xs_s + xo + 32), q3 = lds128(xs_t + xo + 32);
-                                const uint32_t xf[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
-                                                         q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
-                                const uint4 xi = lds128(info_c + (pu + u) * 64);
-                                const uint32_t off = (ubase + u) * UB;
-                                unit_sep<TY>(ta32 + off, tb32 + off, KC, xf, xi, acc);
-                                v += kGemvWarps;
-                                u += kGemvWarps;
-                                while (u >= nu && v < total) { u -= nu; ti++; }
-                            } while (v < total && ti == cur);
-                            // each thread of the quad covered another quarter: add them up
-#pragma unroll
-                            for (int e = 0; e < 2; e++) {
-                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
-                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
-                            }
-                            if (c < 2) dst[g + 8 * c] += c ? acc[1] : acc[0];
-                        } else {
+                        {
                             float acc[2] = {0.f, 0.f};
                             do {
                                 uint32_t xf[16];
@@ -1044,6 +1091,7 @@ __global__ void __launch_bounds__(kGemvThreadsMax, 2) gemv_kernel(GemvArgs p, Ge
                                 dst[(g + 8) * L.nc + c] += acc[1];
                             }
                         }
+                    }
                     }
                     __syncwarp();
                     if (lane == 0) {
@@ -1126,11 +1174,12 @@ static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint3
     if (L.group < 1) L.group = 1;
     if (L.group > tiles_per_cta) L.group = tiles_per_cta;
     const uint32_t red_bytes = L.group * per_tile;
-    const uint32_t tab_bytes = ty == T_IQ2_XXS ? 256 * 8 * tab_copies : 0;
+    const uint32_t tab_bytes = ty == T_IQ2_XXS ? (256 + 128) * 8 * tab_copies : 0;  // codebook and sign masks
     L.tab_copies = tab_copies;
     const uint32_t stage_cap = 46 * 1024;
     const uint32_t row_bytes = nunit * ub;
-    const uint32_t xunit = kXqUnit, info_unit = sep ? 64 : 4 * 48;  // per unit: 4 quarters x float4, or 4 columns x 12 words
+    // per unit: SEP 320 bytes per byte column, records included; WIDE 256 per byte column + 4 columns x 12 words
+    const uint32_t xunit = sep ? kSepUnit : kXqUnit, info_unit = sep ? 0 : 4 * 48;
     // Candidate plans, best first: whole tiles, half tiles, then one copy per row of
     // ever shorter segments (1, 2, ... per row).  Contiguous rows cannot be padded:
     // when the row size is a multiple of 64 bytes the rows a warp reads together
@@ -1170,7 +1219,7 @@ static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint3
         L.rs = rs;
         L.stage_bytes = stage;
         const uint32_t per_chunk = L.ecols * cb * xunit + cb * info_unit;  // x and what goes with it
-        const uint32_t small = kBarBytes + red_bytes + tab_bytes + 64 + L.ecols * 128;
+        const uint32_t small = kBarBytes + red_bytes + tab_bytes + 64 + 128 + L.ecols * 128;
         const uint32_t min_stages = L.mode == 1 ? 4 : 2;
         if (small + min_stages * stage + per_chunk > budget) continue;
         uint32_t nstage, panel;
@@ -1188,8 +1237,8 @@ static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint3
         if (L.mode == 1) nstage &= ~1u;  // a tile takes two stages
         L.nstage = nstage;
         L.panel = panel;
-        L.es = xq_col_stride(panel * cb);
-        L.xs_off = kBarBytes + nstage * stage;
+        L.es = sep ? sep_col_stride(panel * cb) : xq_col_stride(panel * cb);
+        L.xs_off = (kBarBytes + nstage * stage + 127) & ~127u;  // the bank arithmetic of the panel counts from 128
         L.info_off = (L.xs_off + L.ecols * L.es + 15) & ~15u;
         L.red_off = L.info_off + panel * cb * info_unit;
         L.tab_off = (L.red_off + red_bytes + 15) & ~15u;

@@ -169,6 +169,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// The same for the producer thread, which is in no hurry: between polls it sleeps, so that
+// its spinning does not take issue slots from the two consumer warps that share its
+// scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                                  int *status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        __nanosleep(200);
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) break;
+    }
+    *abort_flag = 1;
+    if (status) atomicExch(status, code);
+    return false;
+}
+
 // One-dimensional bulk copy global -> shared; both addresses and the size are
 // multiples of 16 bytes.  Completion is reported to `bar` in bytes.
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
