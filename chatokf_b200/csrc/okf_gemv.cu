@@ -234,7 +234,6 @@ struct SepConst {
     uint32_t sel, m1, m2;   // Q4_K: how to pick this thread's 6-bit scales and mins out of the 12 bytes
     bool low;               // Q4_K: sub-blocks 0..3 (plain 6-bit fields) or 4..7 (split fields)
     uint32_t tab_lane;      // IQ2_XXS: shared address of this lane's copy of codebook entry 0
-    uint32_t sgn_lane;      // IQ2_XXS: the same for the table of sign masks that follows the codebook
     uint32_t tab_stride;    // IQ2_XXS: bytes between table entries (copies of one entry lie side by side)
 };
 template <int TY>
@@ -255,7 +254,6 @@ __device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_
         k.qoff = 2 + 16 * c;
         k.tab_lane = tab + (lane & (tab_copies - 1)) * 8;
         k.tab_stride = tab_copies * 8;
-        k.sgn_lane = k.tab_lane + 256 * k.tab_stride;
     }
     return k;
 }
@@ -381,9 +379,9 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
         // IQ2_XXS {f16 d; 8 x (u32 a0: four codebook indices, u32 a1: four 7-bit sign
         // indices + 4-bit scale)} (LLM/Quantize/IQ2XXS.swift:34-53).  Thread c takes
         // sub-blocks 2c and 2c+1.  A codebook entry is eight magnitude bytes = the two
-        // A registers of one row; the byte masks of a sign index (0xFF = negative) come from
-        // a second table (integer instructions are the scarce resource here, shared-memory
-        // look-ups without bank conflicts are not).  Signs: XOR with the mask turns a
+        // A registers of one row; the byte masks of a sign index (0xFF = negative) are
+        // computed (a table of them, tried, gained 2 % at K = 5120 and cost 8 % at K = 17408,
+        // where it crowds the ring out of shared memory).  Signs: XOR with the mask turns a
         // magnitude m into the signed byte -(m + 1); a second MMA on the masks themselves
         // (255 per negative weight) gives 255 x the sum of x over the negative weights, which
         // puts the missing 1 back: sum(sign * m * x) = D1 + D2 / 255.
@@ -400,8 +398,9 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
             for (int l = 0; l < 4; l++) {
                 const uint2 ea = lds64(K.tab_lane + prmt(a0a, 0u, 0x4440u + l) * K.tab_stride);
                 const uint2 eb = lds64(K.tab_lane + prmt(a0b, 0u, 0x4440u + l) * K.tab_stride);
-                const uint2 ma = lds64(K.sgn_lane + ((a1a >> (7 * l)) & 127u) * K.tab_stride);
-                const uint2 mb = lds64(K.sgn_lane + ((a1b >> (7 * l)) & 127u) * K.tab_stride);
+                uint2 ma, mb;
+                iq2_sign_bytes((a1a >> (7 * l)) & 127u, ma.x, ma.y);
+                iq2_sign_bytes((a1b >> (7 * l)) & 127u, mb.x, mb.y);
                 const uint32_t x0 = xf[8 * sb + 2 * l], x1 = xf[8 * sb + 2 * l + 1];
                 if (l == 0) {
                     imma0<true>(d1, ea.x ^ ma.x, eb.x ^ mb.x, ea.y ^ ma.y, eb.y ^ mb.y, x0, x1);
@@ -837,13 +836,6 @@ __global__ void __launch_bounds__(kGemvThreadsMax, OKF_GEMV_MINB) gemv_kernel(Ge
         uint64_t *tw = reinterpret_cast<uint64_t *>(smem + L.tab_off);
         const uint32_t sh = 31 - __clz(L.tab_copies);
         for (uint32_t i = threadIdx.x; i < 256 * L.tab_copies; i += blockDim.x) tw[i] = g_iq2xxs_grid[i >> sh];
-        // and behind it the byte masks of the 128 sign indices, laid out the same way
-        uint2 *sw = reinterpret_cast<uint2 *>(tw + 256 * L.tab_copies);
-        for (uint32_t i = threadIdx.x; i < 128 * L.tab_copies; i += blockDim.x) {
-            uint2 m;
-            iq2_sign_bytes(i >> sh, m.x, m.y);
-            sw[i] = m;
-        }
     }
     __syncthreads();
 
@@ -1174,7 +1166,7 @@ static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint3
     if (L.group < 1) L.group = 1;
     if (L.group > tiles_per_cta) L.group = tiles_per_cta;
     const uint32_t red_bytes = L.group * per_tile;
-    const uint32_t tab_bytes = ty == T_IQ2_XXS ? (256 + 128) * 8 * tab_copies : 0;  // codebook and sign masks
+    const uint32_t tab_bytes = ty == T_IQ2_XXS ? 256 * 8 * tab_copies : 0;
     L.tab_copies = tab_copies;
     const uint32_t stage_cap = 46 * 1024;
     const uint32_t row_bytes = nunit * ub;
