@@ -1005,85 +1005,90 @@ __global__ void __launch_bounds__(kGemvThreadsMax, OKF_GEMV_MINB) gemv_kernel(Ge
                         rb += ((size_t)min(row + 8, sg.m - 1) * p.row_bytes + (size_t)u0 * UB) & 15;
                     }
                     const uint32_t tile_bytes = 16 * L.rs;
-                    // this warp's units: v = first, first + 8, ... of the step's tn * nu,
-                    // unit v being unit v % nu of tile v / nu
+                    // Integer instructions run at half the rate of the others on this part and the
+                    // unit bodies are full of them, so a warp takes a run of consecutive units of the
+                    // step's tn * nu (unit v being unit v % nu of tile v / nu): the loop over a run
+                    // within one tile is a counter and a few addresses moved by constants, and the
+                    // sums are put away once per run.  The warps that get one unit more than the
+                    // others rotate from step to step.
                     const uint32_t total = tn * nu;
-                    uint32_t v = warp >= rot ? warp - rot : warp + kGemvWarps - rot;
-                    rot = (rot + total) % kGemvWarps;
-                    uint32_t ti = 0, u = v;
-                    while (u >= nu && ti < tn) { u -= nu; ti++; }
+                    const uint32_t wr = warp >= rot ? warp - rot : warp + kGemvWarps - rot;
+                    const uint32_t share = total / kGemvWarps, extra = total % kGemvWarps;
+                    rot = (rot + extra) % kGemvWarps;
+                    uint32_t left = share + (wr < extra ? 1u : 0u);
+                    uint32_t ti = 0, u = wr * share + min(wr, extra);
+                    while (u >= nu && ti + 1 < tn) { u -= nu; ti++; }
                     if constexpr (SEP) {
-                        // Integer instructions run at half the rate of the others on this part and
-                        // the unit bodies are full of them, so the walk over this warp's units
-                        // keeps a handful of addresses and moves them by constants.
                         uint32_t wa = stages32 + (uint32_t)(ra - stages) + ti * tile_bytes + (ubase + u) * UB;  // row g
                         const uint32_t wdelta = (uint32_t)(rb - ra);                                            // to row g + 8
                         uint32_t xa = xbase32 + (pu + u) * xstride32;
                         uint32_t ia = rec32 + (pu + u) * kSepUnit;
                         uint32_t da = red32 + (tl - gb + ti) * (kGemvWarps * 16 * 4);
-                        float acc[2] = {0.f, 0.f};
-                        while (v < total) {
-                            const uint4 q0 = lds128(xa), q1 = lds128(xa + 16), q2 = lds128(xa + 32), q3 = lds128(xa + 48);
-                            const uint32_t xf[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
-                                                     q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
-                            const uint4 xi = lds128(ia);
-                            unit_sep<TY>(wa, wa + wdelta, KC, xf, xi, acc);
-                            v += kGemvWarps;
-                            u += kGemvWarps;
-                            wa += kGemvWarps * UB;
-                            xa += kGemvWarps * xstride32;
-                            ia += kGemvWarps * kSepUnit;
-                            if (u >= nu || v >= total) {
-                                // this warp is through with the tile: each thread of a quad covered
-                                // another quarter; add them up and put the sums into the warp's slot
-#pragma unroll
-                                for (int e = 0; e < 2; e++) {
-                                    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
-                                    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
-                                }
-                                if (c < 2) sts32(da, __float_as_uint(__uint_as_float(lds32(da)) + (c ? acc[1] : acc[0])));
-                                acc[0] = acc[1] = 0.f;
-                                while (u >= nu) {  // on to the next tile (more than one when a tile has few units)
-                                    u -= nu;
-                                    wa += tile_bytes - nu * UB;
-                                    xa -= nu * xstride32;
-                                    ia -= nu * kSepUnit;
-                                    da += kGemvWarps * 16 * 4;
-                                }
+                        while (left) {
+                            const uint32_t run = min(left, nu - u);  // the rest of this tile, or of the share
+                            left -= run;
+                            float acc[2] = {0.f, 0.f};
+#pragma unroll 1
+                            for (uint32_t i = run; i; i--) {
+                                const uint4 q0 = lds128(xa), q1 = lds128(xa + 16), q2 = lds128(xa + 32), q3 = lds128(xa + 48);
+                                const uint32_t xf[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
+                                                         q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+                                const uint4 xi = lds128(ia);
+                                unit_sep<TY>(wa, wa + wdelta, KC, xf, xi, acc);
+                                wa += UB;
+                                xa += xstride32;
+                                ia += kSepUnit;
                             }
+                            // each thread of a quad covered another quarter: add them up and put the
+                            // sums into the warp's slot of the tile
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+                                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+                            }
+                            if (c < 2) sts32(da, __float_as_uint(__uint_as_float(lds32(da)) + (c ? acc[1] : acc[0])));
+                            // on to the first unit of the next tile
+                            u = 0;
+                            wa += tile_bytes - nu * UB;
+                            xa -= nu * xstride32;
+                            ia -= nu * kSepUnit;
+                            da += kGemvWarps * 16 * 4;
                         }
                     } else {
-                    while (v < total) {
-                        const uint32_t cur = ti;
-                        const uint8_t *ta = ra + (size_t)cur * tile_bytes, *tb = rb + (size_t)cur * tile_bytes;
-                        // this warp's own slot of the tile's partial sums
-                        float *dst = red + ((size_t)(tl - gb + cur) * kGemvWarps + warp) * 16 * L.nc;
-                        {
+                        // lanes of columns that do not exist read column 0's record; their sums are dropped
+                        const float *xw0 = reinterpret_cast<const float *>(info) + (c < L.nc ? c : 0) * 12;
+                        while (left) {
+                            const uint32_t run = min(left, nu - u);
+                            left -= run;
+                            const uint8_t *ta = ra + (size_t)ti * tile_bytes + (size_t)(ubase + u) * UB;
+                            const uint32_t tdelta = (uint32_t)(rb - ra);
+                            const uint8_t *xp = xs_mine + (pu + u) * xs_ustride;
+                            const float *xw = xw0 + (size_t)(pu + u) * 48;
                             float acc[2] = {0.f, 0.f};
-                            do {
+#pragma unroll 1
+                            for (uint32_t i = run; i; i--) {
                                 uint32_t xf[16];
-                                const uint8_t *xp = xs_mine + (pu + u) * xs_ustride;
 #pragma unroll
                                 for (int q = 0; q < 4; q++) {
                                     uint4 w4 = make_uint4(0u, 0u, 0u, 0u);
                                     if (x_active) w4 = lds128(xp + (q >> 1) * 32 + ((q & 1) ? 16 - xq_swap : xq_swap));
                                     xf[4 * q] = w4.x; xf[4 * q + 1] = w4.y; xf[4 * q + 2] = w4.z; xf[4 * q + 3] = w4.w;
                                 }
-                                const uint32_t off = (ubase + u) * UB;
-                                // lanes of columns that do not exist read column 0's record; their sums are dropped
-                                const float *xw = reinterpret_cast<const float *>(info) + ((size_t)(pu + u) * 4 + (c < L.nc ? c : 0)) * 12;
-                                unit_wide<TY>(ta + off, tb + off, c, xf, xw, tab, L.tab_copies, acc);
-                                v += kGemvWarps;
-                                u += kGemvWarps;
-                                while (u >= nu && v < total) { u -= nu; ti++; }
-                            } while (v < total && ti == cur);
-                            // thread (g, c) holds the finished sums of rows g, g + 8 for column c
+                                unit_wide<TY>(ta, ta + tdelta, c, xf, xw, tab, L.tab_copies, acc);
+                                ta += UB;
+                                xp += xs_ustride;
+                                xw += 48;
+                            }
+                            // thread (g, c) holds the sums of rows g, g + 8 for column c: into this
+                            // warp's own slot of the tile's partial sums
                             if (c < L.nc) {
+                                float *dst = red + ((size_t)(tl - gb + ti) * kGemvWarps + warp) * 16 * L.nc;
                                 dst[g * L.nc + c] += acc[0];
                                 dst[(g + 8) * L.nc + c] += acc[1];
                             }
+                            u = 0;
+                            ti++;
                         }
-                    }
                     }
                     __syncwarp();
                     if (lane == 0) {
