@@ -10,8 +10,11 @@
 //     map of X, already in the 128-byte-swizzled K-major layout the tensor core
 //     reads (fp32 activations are converted by eight warps instead);
 //   - two groups of eight warps, taking the k-blocks in turn, unpack 128 rows x 64
-//     weights to 16-bit floats into the same layout; weight bytes are fetched one
-//     turn ahead;
+//     weights to 16-bit floats into the same layout.  Q4_K slabs come by TMA as well,
+//     as they are stored, 128 rows x one 144-byte block (four k-blocks) per copy into
+//     a ring of their own, so the unpacking reads shared memory and never waits for
+//     global memory; the other types' blocks do not start on 16-byte boundaries and
+//     are fetched by the unpacking threads one turn ahead;
 //   - one thread issues four tcgen05.mma (M = 128, N = 256, K = 16) per token block
 //     that accumulate in fp32 in tensor memory: lane = weight row, column = token;
 //   - tcgen05.commit hands the stage back to the producers when the MMAs that
@@ -52,12 +55,17 @@ constexpr uint32_t kProducerWarps = kAWarps + kBWarps;
 constexpr uint32_t kTmaWarp = kProducerWarps;          // warp 16: one thread hands B tiles to the copy engine
 constexpr uint32_t kMmaWarp = kProducerWarps + 1;      // warp 17
 constexpr uint32_t kThreads = (kProducerWarps + 2 + 4) * 32;  // + four epilogue warps
+// Q4_K: a third ring holds the weights as stored: a stage is 128 rows x one block of 144 bytes.
+template <int TY> constexpr bool kRawByTma = TY == T_Q4_K;
+constexpr uint32_t kRawBlock = 144, kRawBytes = kBM * kRawBlock, kRawKBlocks = 256 / kBK;  // 18 KB = four k-blocks
 template <int TY, int NACC> struct Rings {
+    static constexpr uint32_t raw_stages = kRawByTma<TY> ? 3 : 0;
     static constexpr uint32_t a_stages = NACC == 2 ? 2 : 4;
-    static constexpr uint32_t b_stages = NACC == 2 ? (TY == T_IQ2_XXS ? 2 : 3) : 4;
+    static constexpr uint32_t b_stages = NACC == 2 ? (TY == T_IQ2_XXS || kRawByTma<TY> ? 2 : 3) : (kRawByTma<TY> ? 3 : 4);
     static constexpr uint32_t a_bytes = a_stages * kABytes, b_stage = NACC * kBBytes, b_bytes = b_stages * b_stage;
+    static constexpr uint32_t raw_bytes = raw_stages * kRawBytes;
     static constexpr uint32_t grid_bytes = TY == T_IQ2_XXS ? 2048 : 0;
-    static constexpr uint32_t smem = 1024 /*align*/ + a_bytes + b_bytes + grid_bytes + 256 /*barriers*/;
+    static constexpr uint32_t smem = 1024 /*align*/ + a_bytes + b_bytes + raw_bytes + grid_bytes + 256 /*barriers*/;
 };
 constexpr int kStatusGemmTimeout = 3;
 
@@ -207,6 +215,13 @@ template <> struct ARaw<T_Q4_K> {
         q1 = __ldg(reinterpret_cast<const uint4 *>(b + 32 + 32 * (kb & 3)));
         j = (kb & 3) * 2 + h;
     }
+    // the same out of a block that lies in shared memory
+    __device__ __forceinline__ void take(const uint8_t *b, uint32_t kb, uint32_t h) {
+        hdr = *reinterpret_cast<const uint4 *>(b);
+        q0 = *reinterpret_cast<const uint4 *>(b + 16 + 32 * (kb & 3));
+        q1 = *reinterpret_cast<const uint4 *>(b + 32 + 32 * (kb & 3));
+        j = (kb & 3) * 2 + h;
+    }
     // w = (d * sc) * q - dmin * m (LLM/Quantize/KQuants.swift:104-125), here with one
     // fused multiply-add: the result is rounded to a 16-bit float anyway
     __device__ __forceinline__ void decode(float (&v)[32], const uint64_t *) const {
@@ -310,21 +325,26 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32
 template <int TY, int XDT, typename OT, int NACC>
 // (The tensor map comes first so that its 128 bytes start on a 128-byte boundary of the
 // parameter block whatever the size of Args: measured 12 % slower when it straddled one.)
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Args p, Outs go) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                              const __grid_constant__ CUtensorMap wmap, Args p, Outs go) {
     constexpr bool F16 = XDT == DT_F16;
     constexpr bool ASYNC_B = XDT != DT_F32;  // 16-bit activations come by TMA, fp32 ones are converted by eight warps
+    constexpr bool RAW = kRawByTma<TY>;      // the weights come by TMA too, as stored
     using R = Rings<TY, NACC>;
     constexpr uint32_t kAStages = R::a_stages, kBStages = R::b_stages, kBStage = R::b_stage;
+    constexpr uint32_t kRawStages = RAW ? R::raw_stages : 1;
+    constexpr uint32_t kGroups = ASYNC_B ? 2 : 1;  // groups of eight unpacking warps
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *a_ring = smem, *b_ring = smem + R::a_bytes;
-    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes + R::grid_bytes);
+    uint8_t *a_ring = smem, *b_ring = smem + R::a_bytes, *raw_ring = smem + R::a_bytes + R::b_bytes;
+    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes + R::raw_bytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes + R::raw_bytes + R::grid_bytes);
     uint64_t *full_a = bars, *empty_a = bars + 4;      // A producers <-> MMA, one pair per A stage
     uint64_t *full_b = bars + 8, *empty_b = bars + 12;  // B producer(s) <-> MMA, one pair per B stage
     uint64_t *acc_full = bars + 16;            // MMA -> epilogue, one per accumulator
     uint64_t *acc_empty = acc_full + 2;        // epilogue -> MMA
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    uint64_t *raw_full = bars + 20, *raw_empty = bars + 24;  // copy engine <-> unpacking warps, one pair per raw stage
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 28);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -340,6 +360,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         for (uint32_t a = 0; a < 2; a++) {
             mbar_init(&acc_full[a], 1);
             mbar_init(&acc_empty[a], 4);
+        }
+        if constexpr (RAW) {
+            for (uint32_t s = 0; s < kRawStages; s++) {
+                mbar_init(&raw_full[s], 1);
+                mbar_init(&raw_empty[s], kGroups * kAWarps);
+            }
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -362,69 +388,110 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         // With 16-bit activations there are two groups of eight warps that take the k-blocks
         // in turn: one k-block's latency (load, decode, wait, store, fence) is longer than the
         // MMAs it feeds, two in flight are not.
-        constexpr uint32_t kGroups = ASYNC_B ? 2 : 1;
         const uint32_t grp = warp / kAWarps;
         const uint32_t t = threadIdx.x % (kAWarps * 32);
         const uint32_t arow = t >> 1, ahalf = t & 1;  // thread t unpacks 32 weights of row arow
         uint32_t it0 = 0;  // stage counter at the start of the work item
+        [[maybe_unused]] uint32_t rit = 0;  // raw stages taken so far
         Work wk;
+        // decoded values -> 16-bit floats -> this thread's four 16-byte chunks of stage s
+        auto put = [&](const float (&v)[32], bool live, uint32_t it) -> bool {
+            const uint32_t s = it % kAStages, use = it / kAStages;
+            uint4 q[4];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) {
+                q[c4].x = live ? pack16<F16>(v[8 * c4], v[8 * c4 + 1]) : 0u;
+                q[c4].y = live ? pack16<F16>(v[8 * c4 + 2], v[8 * c4 + 3]) : 0u;
+                q[c4].z = live ? pack16<F16>(v[8 * c4 + 4], v[8 * c4 + 5]) : 0u;
+                q[c4].w = live ? pack16<F16>(v[8 * c4 + 6], v[8 * c4 + 7]) : 0u;
+            }
+            if (use > 0 && !warp_wait(&empty_a[s], (use - 1) & 1, lane, abort_flag, p.status)) return false;
+            uint8_t *sa = a_ring + (size_t)s * kABytes;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) *reinterpret_cast<uint4 *>(sa + swz(arow, ahalf * 4 + c4)) = q[c4];
+            fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_a[s]);
+            return true;
+        };
         for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
             const uint32_t m0 = wk.mt * kBM;
             const uint32_t kb0 = wk.kb0, kb1 = wk.kb1;
-            const uint32_t wrow = min(m0 + arow, p.m - 1);
-            const uint8_t *wp = p.w + (size_t)wrow * p.row_bytes;
             const bool arow_live = m0 + arow < p.m;
-            // this group's first k-block: the one whose stage counter has its parity
-            const uint32_t first = kb0 + (kGroups == 2 ? ((grp + it0) & 1) : 0);
-            ARaw<TY> cur, nxt;
-            if (first < kb1) cur.load(wp, first, ahalf);
-            for (uint32_t kb = first; kb < kb1; kb += kGroups) {
-                const uint32_t it = it0 + (kb - kb0);
-                const uint32_t s = it % kAStages, use = it / kAStages;
-                if (kb + kGroups < kb1) nxt.load(wp, kb + kGroups, ahalf);
-                float v[32];
-                cur.decode(v, grid);
-                uint4 q[4];
-#pragma unroll
-                for (int c4 = 0; c4 < 4; c4++) {
-                    q[c4].x = arow_live ? pack16<F16>(v[8 * c4], v[8 * c4 + 1]) : 0u;
-                    q[c4].y = arow_live ? pack16<F16>(v[8 * c4 + 2], v[8 * c4 + 3]) : 0u;
-                    q[c4].z = arow_live ? pack16<F16>(v[8 * c4 + 4], v[8 * c4 + 5]) : 0u;
-                    q[c4].w = arow_live ? pack16<F16>(v[8 * c4 + 6], v[8 * c4 + 7]) : 0u;
+            if constexpr (RAW) {
+                // one raw stage = block column jb = the k-blocks 4 jb .. 4 jb + 3 of the 128 rows; both
+                // groups wait for it, unpack their k-blocks out of it and hand it back
+                for (uint32_t jb = kb0 / kRawKBlocks; jb <= (kb1 - 1) / kRawKBlocks; jb++, rit++) {
+                    const uint32_t rs = rit % kRawStages;
+                    if (!warp_wait(&raw_full[rs], (rit / kRawStages) & 1, lane, abort_flag, p.status)) goto done;
+                    const uint8_t *blk = raw_ring + (size_t)rs * kRawBytes + arow * kRawBlock;
+                    const uint32_t lo = max(kb0, jb * kRawKBlocks), hi = min(kb1, (jb + 1) * kRawKBlocks);
+                    for (uint32_t kb = lo; kb < hi; kb++) {
+                        const uint32_t it = it0 + (kb - kb0);
+                        if (kGroups == 2 && (it & 1) != grp) continue;
+                        ARaw<TY> cur;
+                        cur.take(blk, kb, ahalf);
+                        float v[32];
+                        cur.decode(v, grid);
+                        if (!put(v, arow_live, it)) goto done;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&raw_empty[rs]);
                 }
-                if (use > 0 && !warp_wait(&empty_a[s], (use - 1) & 1, lane, abort_flag, p.status)) goto done;
-                uint8_t *sa = a_ring + (size_t)s * kABytes;
-#pragma unroll
-                for (int c4 = 0; c4 < 4; c4++) *reinterpret_cast<uint4 *>(sa + swz(arow, ahalf * 4 + c4)) = q[c4];
-                fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full_a[s]);
-                cur = nxt;
+            } else {
+                const uint32_t wrow = min(m0 + arow, p.m - 1);
+                const uint8_t *wp = p.w + (size_t)wrow * p.row_bytes;
+                // this group's first k-block: the one whose stage counter has its parity
+                const uint32_t first = kb0 + (kGroups == 2 ? ((grp + it0) & 1) : 0);
+                ARaw<TY> cur, nxt;
+                if (first < kb1) cur.load(wp, first, ahalf);
+                for (uint32_t kb = first; kb < kb1; kb += kGroups) {
+                    if (kb + kGroups < kb1) nxt.load(wp, kb + kGroups, ahalf);
+                    float v[32];
+                    cur.decode(v, grid);
+                    if (!put(v, arow_live, it0 + (kb - kb0))) goto done;
+                    cur = nxt;
+                }
             }
             it0 += kb1 - kb0;
         }
     } else if (warp == kTmaWarp) {
-        // ---------------- B tiles of 16-bit activations: NACC x 256 tokens x 64 k per stage
-        if constexpr (ASYNC_B) {
-            if (lane == 0) {
-                uint32_t it = 0;
-                Work wk;
-                for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
-                    const uint32_t nblk = wk.ntok > kBN ? NACC : 1;
-                    for (uint32_t kb = wk.kb0; kb < wk.kb1; kb++, it++) {
-                        const uint32_t s = it % kBStages, use = it / kBStages;
-                        if (use > 0 && !mbar_wait(&empty_b[s], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
-                            // giving up: the copies already handed over land within microseconds;
-                            // stay for a while so that they do not write into a CTA that has gone
-                            const long long t0 = clock64();
-                            while (clock64() - t0 < 100000) {}
-                            goto done;
-                        }
-                        uint8_t *sb = b_ring + (size_t)s * kBStage;
-                        mbar_expect_tx(&full_b[s], nblk * kBBytes);
-                        for (uint32_t a = 0; a < nblk; a++)
-                            tma_load_tile(sb + a * kBBytes, &xmap, kb * kBK, wk.n0 + a * kBN, &full_b[s]);
+        // ---------------- the copy engine's two clients, one thread each
+        if (ASYNC_B && lane == 0) {
+            // B tiles of 16-bit activations: NACC x 256 tokens x 64 k per stage
+            uint32_t it = 0;
+            Work wk;
+            for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
+                const uint32_t nblk = wk.ntok > kBN ? NACC : 1;
+                for (uint32_t kb = wk.kb0; kb < wk.kb1; kb++, it++) {
+                    const uint32_t s = it % kBStages, use = it / kBStages;
+                    if (use > 0 && !mbar_wait(&empty_b[s], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
+                        // giving up: the copies already handed over land within microseconds;
+                        // stay for a while so that they do not write into a CTA that has gone
+                        const long long t0 = clock64();
+                        while (clock64() - t0 < 100000) {}
+                        goto done;
                     }
+                    uint8_t *sb = b_ring + (size_t)s * kBStage;
+                    mbar_expect_tx(&full_b[s], nblk * kBBytes);
+                    for (uint32_t a = 0; a < nblk; a++)
+                        tma_load_tile(sb + a * kBBytes, &xmap, kb * kBK, wk.n0 + a * kBN, &full_b[s]);
+                }
+            }
+        } else if (RAW && lane == 1) {
+            // the weights as stored: block column jb of the item's 128 rows, rows past M as zeros
+            uint32_t rit = 0;
+            Work wk;
+            for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
+                for (uint32_t jb = wk.kb0 / kRawKBlocks; jb <= (wk.kb1 - 1) / kRawKBlocks; jb++, rit++) {
+                    const uint32_t rs = rit % kRawStages, use = rit / kRawStages;
+                    if (use > 0 && !mbar_wait(&raw_empty[rs], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
+                        const long long t0 = clock64();
+                        while (clock64() - t0 < 100000) {}
+                        goto done;
+                    }
+                    mbar_expect_tx(&raw_full[rs], kRawBytes);
+                    tma_load_tile(raw_ring + (size_t)rs * kRawBytes, &wmap, jb * kRawBlock, wk.mt * kBM, &raw_full[rs]);
                 }
             }
         }
@@ -489,8 +556,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             uint32_t it = 0, tile = 0;
             Work wk;
             for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++, tile++) {
-                // N of the instruction: a whole block, or the tokens of a short run
-                const uint32_t idesc = instr_desc(F16 ? 0u : 1u, kBM, wk.ntok < kBN ? wk.ntok : kBN);
+                // N of the instruction: the tokens each block of the item really has, in sixteens
+                const uint32_t live = min(wk.ntok, p.n - wk.n0);
+                uint32_t idesc[NACC];
+#pragma unroll
+                for (uint32_t a = 0; a < (uint32_t)NACC; a++) {
+                    const uint32_t nt = live > a * kBN ? min(live - a * kBN, kBN) : 0u;
+                    idesc[a] = instr_desc(F16 ? 0u : 1u, kBM, nt ? (nt + 15u) & ~15u : 16u);
+                }
                 // accumulators: both for a two-block item, alternating for one-block items
                 const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
                 bool ok = true;
@@ -516,7 +589,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
                         for (uint32_t k4 = 0; k4 < kBK / 16; k4++) {
                             // 16 k = 32 bytes further along the swizzled 128-byte row
-                            umma(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                            umma(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc[a], (kb != kb0 || k4 != 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&empty_a[s_a]);  // both stages are free once these MMAs have read them
@@ -641,9 +714,10 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
     if (o.epoch && blockIdx.x == 0 && threadIdx.x == 0) o.epoch[0] += o.epoch_inc;
 }
 
-// Tensor map of the activations X[n][k] (16-bit elements) for tma_load_tile.  The
-// driver's encoder is looked up once; nothing is linked against libcuda.
-static cudaError_t encode_x_map(CUtensorMap *map, const void *x, uint32_t k, uint32_t n) {
+// Tensor maps for tma_load_tile.  The driver's encoder is looked up once; nothing is linked
+// against libcuda.  2-D, element size 1 or 2 bytes: dims / box in elements, stride in bytes.
+static cudaError_t encode_map_2d(CUtensorMap *map, bool bytes, const void *base, uint64_t dim0, uint64_t dim1,
+                                 uint64_t stride, uint32_t box0, uint32_t box1, bool swizzle128) {
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -656,14 +730,23 @@ static cudaError_t encode_x_map(CUtensorMap *map, const void *x, uint32_t k, uin
         if (q != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
         encode = (EncodeFn)fn;
     }
-    const cuuint64_t dims[2] = {k, n};
-    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    const cuuint32_t box[2] = {kBK, kBN};
+    const cuuint64_t dims[2] = {dim0, dim1};
+    const cuuint64_t strides[1] = {stride};
+    const cuuint32_t box[2] = {box0, box1};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(x), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    const CUresult r = encode(map, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                              const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+// the activations X[n][k], 16-bit elements: 64 k x 256 tokens per copy, swizzled as the MMA reads them
+static cudaError_t encode_x_map(CUtensorMap *map, const void *x, uint32_t k, uint32_t n) {
+    return encode_map_2d(map, false, x, k, n, (uint64_t)k * 2, kBK, kBN, true);
+}
+// Q4_K weights W[m][row_bytes] as bytes: one 144-byte block x 128 rows per copy, as stored
+static cudaError_t encode_w_map(CUtensorMap *map, const void *w, uint32_t row_bytes, uint32_t m) {
+    return encode_map_2d(map, true, w, row_bytes, m, row_bytes, kRawBlock, kBM, false);
 }
 
 template <int TY, int XDT, typename OT, int NACC>
@@ -683,7 +766,13 @@ static cudaError_t launch_n(const Args &a, const Outs &go, cudaStream_t s, int s
         cudaError_t me = encode_x_map(&xmap, a.x, a.k, a.n);
         if (me != cudaSuccess) return me;
     }
-    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, Rings<TY, NACC>::smem, s>>>(xmap, a, go);
+    alignas(64) CUtensorMap wmap;
+    memset(&wmap, 0, sizeof(wmap));
+    if constexpr (kRawByTma<TY>) {
+        cudaError_t me = encode_w_map(&wmap, a.w, a.row_bytes, a.m);
+        if (me != cudaSuccess) return me;
+    }
+    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, Rings<TY, NACC>::smem, s>>>(xmap, wmap, a, go);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || a.ksplit == 1) return e;
     const size_t count = (size_t)a.n * a.m;
