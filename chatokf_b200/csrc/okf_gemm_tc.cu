@@ -10,11 +10,9 @@
 //     map of X, already in the 128-byte-swizzled K-major layout the tensor core
 //     reads (fp32 activations are converted by eight warps instead);
 //   - two groups of eight warps, taking the k-blocks in turn, unpack 128 rows x 64
-//     weights to 16-bit floats into the same layout.  Q4_K slabs come by TMA as well,
-//     as they are stored, 128 rows x one 144-byte block (four k-blocks) per copy into
-//     a ring of their own, so the unpacking reads shared memory and never waits for
-//     global memory; the other types' blocks do not start on 16-byte boundaries and
-//     are fetched by the unpacking threads one turn ahead;
+//     weights to 16-bit floats into the same layout; weight bytes are fetched one
+//     or two turns ahead.  (Bringing Q4_K slabs in by TMA as stored, 128 rows x one
+//     144-byte block per copy into a ring of their own, was tried and was slower.)
 //   - one thread issues four tcgen05.mma (M = 128, N = 256, K = 16) per token block
 //     that accumulate in fp32 in tensor memory: lane = weight row, column = token;
 //   - tcgen05.commit hands the stage back to the producers when the MMAs that
@@ -55,17 +53,14 @@ constexpr uint32_t kProducerWarps = kAWarps + kBWarps;
 constexpr uint32_t kTmaWarp = kProducerWarps;          // warp 16: one thread hands B tiles to the copy engine
 constexpr uint32_t kMmaWarp = kProducerWarps + 1;      // warp 17
 constexpr uint32_t kThreads = (kProducerWarps + 2 + 4) * 32;  // + four epilogue warps
-// Q4_K: a third ring holds the weights as stored: a stage is 128 rows x one block of 144 bytes.
-template <int TY> constexpr bool kRawByTma = TY == T_Q4_K;
-constexpr uint32_t kRawBlock = 144, kRawBytes = kBM * kRawBlock, kRawKBlocks = 256 / kBK;  // 18 KB = four k-blocks
+constexpr uint32_t kMaxRing = 4;                                      // stages a ring may have
+constexpr uint32_t kBarRegion = 256;                                  // barriers, tensor-memory slot, abort flag
 template <int TY, int NACC> struct Rings {
-    static constexpr uint32_t raw_stages = kRawByTma<TY> ? 3 : 0;
     static constexpr uint32_t a_stages = NACC == 2 ? 2 : 4;
-    static constexpr uint32_t b_stages = NACC == 2 ? (TY == T_IQ2_XXS || kRawByTma<TY> ? 2 : 3) : (kRawByTma<TY> ? 3 : 4);
+    static constexpr uint32_t b_stages = NACC == 2 ? (TY == T_IQ2_XXS ? 2 : 3) : 4;
     static constexpr uint32_t a_bytes = a_stages * kABytes, b_stage = NACC * kBBytes, b_bytes = b_stages * b_stage;
-    static constexpr uint32_t raw_bytes = raw_stages * kRawBytes;
     static constexpr uint32_t grid_bytes = TY == T_IQ2_XXS ? 2048 : 0;
-    static constexpr uint32_t smem = 1024 /*align*/ + a_bytes + b_bytes + raw_bytes + grid_bytes + 256 /*barriers*/;
+    static constexpr uint32_t smem = 1024 /*align*/ + a_bytes + b_bytes + grid_bytes + kBarRegion;
 };
 constexpr int kStatusGemmTimeout = 3;
 
@@ -201,47 +196,59 @@ __device__ __forceinline__ uint32_t pack16(float a, float b) {
 // decode() so the memory latency hides behind the previous block's work.
 // Q4_K and Q2_0 (the prefill shapes that are benchmarked) have register
 // forms; the other types unpack straight from memory with decode32.
+// Which 16-byte chunk of the row's 128 bytes (64 k) the thread's c4-th group of eight values is.
+__device__ __forceinline__ uint32_t chunk_in_order(uint32_t h, uint32_t c4) { return h * 4 + c4; }
+
 template <int TY> struct ARaw {
+    static constexpr int kAhead = 1;  // k-blocks of this thread in flight beside the one being unpacked
+    __device__ static __forceinline__ uint32_t chunk(uint32_t h, uint32_t c4) { return chunk_in_order(h, c4); }
     const uint8_t *wp; uint32_t gran;
     __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) { wp = row; gran = kb * 2 + h; }
     __device__ __forceinline__ void decode(float (&v)[32], const uint64_t *grid) const { decode32<TY>(wp, gran, v, grid); }
 };
+// Q4_K: a k-block is 32 bytes of a 144-byte block: low nibbles = its first 32 weights (sub-block
+// 2p), high nibbles = the other 32 (sub-block 2p + 1).  The two threads of a row take 16 bytes
+// each and unpack both nibbles, so a thread fetches 32 bytes per k-block, header included, and
+// can afford to fetch two k-blocks ahead: one turn ahead does not cover the latency of L2.
 template <> struct ARaw<T_Q4_K> {
-    uint4 hdr, q0, q1; uint32_t j;  // j: sub-block index 0..7
+    static constexpr int kAhead = 2;
+    // values 0..15 are k = 16h + 0..15 (chunks 2h, 2h + 1), values 16..31 the same positions 32 further on
+    __device__ static __forceinline__ uint32_t chunk(uint32_t h, uint32_t c4) { return (c4 >> 1) * 4 + 2 * h + (c4 & 1); }
+    uint4 hdr, q; uint32_t p;  // p: which 32 bytes of the block's 128
     __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) {
         const uint8_t *b = row + (size_t)(kb >> 2) * 144;
         hdr = __ldg(reinterpret_cast<const uint4 *>(b));
-        q0 = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 32 * (kb & 3)));
-        q1 = __ldg(reinterpret_cast<const uint4 *>(b + 32 + 32 * (kb & 3)));
-        j = (kb & 3) * 2 + h;
-    }
-    // the same out of a block that lies in shared memory
-    __device__ __forceinline__ void take(const uint8_t *b, uint32_t kb, uint32_t h) {
-        hdr = *reinterpret_cast<const uint4 *>(b);
-        q0 = *reinterpret_cast<const uint4 *>(b + 16 + 32 * (kb & 3));
-        q1 = *reinterpret_cast<const uint4 *>(b + 32 + 32 * (kb & 3));
-        j = (kb & 3) * 2 + h;
+        q = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 32 * (kb & 3) + 16 * h));
+        p = kb & 3;
     }
     // w = (d * sc) * q - dmin * m (LLM/Quantize/KQuants.swift:104-125), here with one
     // fused multiply-add: the result is rounded to a 16-bit float anyway
     __device__ __forceinline__ void decode(float (&v)[32], const uint64_t *) const {
-        const uint32_t s32[3] = {hdr.y, hdr.z, hdr.w};
-        auto sbyte = [&](uint32_t i) { return (s32[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
-        uint32_t sc, mn;
-        if (j < 4) { sc = sbyte(j) & 63u; mn = sbyte(j + 4) & 63u; }
-        else { sc = (sbyte(j + 4) & 0xFu) | ((sbyte(j - 4) >> 6) << 4); mn = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4); }
-        const float d1 = f16bits(hdr.x & 0xFFFF) * (float)sc, o1 = f16bits(hdr.x >> 16) * (float)mn;
-        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        const uint32_t sh = (j & 1) * 4;
+        // 6-bit scales and mins of sub-blocks 2p and 2p + 1 (get_scale_min_k4): bytes 2p, 2p + 1 of
+        // the scale field for p < 2, split fields above
+        const uint32_t sh = (p & 1) * 16;
+        const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, e = hdr.w >> sh;
+        uint32_t sc, mn;  // two bytes each: sub-block 2p, 2p + 1
+        if (p < 2) { sc = a & 0x3F3Fu; mn = b & 0x3F3Fu; }
+        else { sc = (e & 0x0F0Fu) | ((a >> 2) & 0x3030u); mn = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u); }
+        const float d = f16bits(hdr.x & 0xFFFF), dm = f16bits(hdr.x >> 16);
+        const float d0 = d * byte_to_f32(sc, 0), d1 = d * byte_to_f32(sc, 1);
+        const float o0 = dm * byte_to_f32(mn, 0), o1 = dm * byte_to_f32(mn, 1);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const uint32_t t = (w[i] >> sh) & 0x0F0F0F0Fu;
+        for (int i = 0; i < 4; i++) {
+            const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
-            for (int e = 0; e < 4; e++) v[4 * i + e] = fmaf(d1, byte_to_f32(t, e), -o1);
+            for (int e4 = 0; e4 < 4; e4++) {
+                v[4 * i + e4] = fmaf(d0, byte_to_f32(lo, e4), -o0);
+                v[16 + 4 * i + e4] = fmaf(d1, byte_to_f32(hi, e4), -o1);
+            }
         }
     }
 };
 template <> struct ARaw<T_Q8_0> {
+    static constexpr int kAhead = 1;
+    __device__ static __forceinline__ uint32_t chunk(uint32_t h, uint32_t c4) { return chunk_in_order(h, c4); }
     uint32_t w[10], sh;  // the 34-byte block {f16 d; i8 q[32]} and what precedes it in its first word
     __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) {
         const uint8_t *b = row + (size_t)(kb * 2 + h) * 34;  // 2-byte aligned
@@ -264,6 +271,8 @@ template <> struct ARaw<T_Q8_0> {
     }
 };
 template <> struct ARaw<T_Q2_0> {
+    static constexpr int kAhead = 1;
+    __device__ static __forceinline__ uint32_t chunk(uint32_t h, uint32_t c4) { return chunk_in_order(h, c4); }
     uint32_t c0, c1, dbits;  // 32 two-bit codes and the block scale
     __device__ __forceinline__ void load(const uint8_t *row, uint32_t kb, uint32_t h) {
         const uint8_t *b = row + (size_t)(kb >> 1) * 34;           // block of 128 weights
@@ -302,49 +311,67 @@ __device__ __forceinline__ void tma_load_tile(void *dst, const CUtensorMap *map,
         : "memory");
 }
 
-// One lane polls, the warp follows.  Producers that run ahead sleep between polls
-// so they do not take issue slots from the warps doing the unpacking.
+// Waiting on an mbarrier without taking issue slots from the unpacking warps: try_wait with
+// a time hint parks the thread in hardware until the phase completes or the hint runs out,
+// so a waiter costs a handful of instructions per microsecond instead of a polling loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// The phase was not over at the first look.  Bounded (about a second): a wait that gives
+// up sets the CTA's abort flag and the status word.
+__device__ __noinline__ bool mbar_wait_parked(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16; i++)
+            if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) break;
+    }
+    *abort_flag = 1;
+    if (status) atomicExch(status, kStatusGemmTimeout);
+    return false;
+}
+// One lane waits, the warp follows.
 __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, uint32_t lane, volatile int *abort_flag,
                                           int *status) {
     bool ok = true;
-    if (lane == 0) {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(bar, parity)) {
-            __nanosleep(40);
-            if (*abort_flag || clock64() - t0 > kWaitCycles) {
-                if (!*abort_flag) { *abort_flag = 1; if (status) atomicExch(status, kStatusGemmTimeout); }
-                ok = false;
-                break;
-            }
-        }
-    }
+    if (lane == 0 && !mbar_try_wait(bar, parity)) ok = mbar_wait_parked(bar, parity, abort_flag, status);
     return __shfl_sync(0xffffffffu, ok, 0);
+}
+// a single thread (the MMA issuer, the copy engine's clients)
+__device__ __forceinline__ bool thread_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    return mbar_try_wait(bar, parity) || mbar_wait_parked(bar, parity, abort_flag, status);
 }
 
 // NACC: token blocks (accumulators) per work item, 1 or 2.
 template <int TY, int XDT, typename OT, int NACC>
 // (The tensor map comes first so that its 128 bytes start on a 128-byte boundary of the
 // parameter block whatever the size of Args: measured 12 % slower when it straddled one.)
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap,
-                                                              const __grid_constant__ CUtensorMap wmap, Args p, Outs go) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Args p, Outs go) {
     constexpr bool F16 = XDT == DT_F16;
     constexpr bool ASYNC_B = XDT != DT_F32;  // 16-bit activations come by TMA, fp32 ones are converted by eight warps
-    constexpr bool RAW = kRawByTma<TY>;      // the weights come by TMA too, as stored
     using R = Rings<TY, NACC>;
     constexpr uint32_t kAStages = R::a_stages, kBStages = R::b_stages, kBStage = R::b_stage;
-    constexpr uint32_t kRawStages = RAW ? R::raw_stages : 1;
     constexpr uint32_t kGroups = ASYNC_B ? 2 : 1;  // groups of eight unpacking warps
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *a_ring = smem, *b_ring = smem + R::a_bytes, *raw_ring = smem + R::a_bytes + R::b_bytes;
-    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes + R::raw_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes + R::raw_bytes + R::grid_bytes);
-    uint64_t *full_a = bars, *empty_a = bars + 4;      // A producers <-> MMA, one pair per A stage
-    uint64_t *full_b = bars + 8, *empty_b = bars + 12;  // B producer(s) <-> MMA, one pair per B stage
-    uint64_t *acc_full = bars + 16;            // MMA -> epilogue, one per accumulator
+    uint8_t *a_ring = smem, *b_ring = smem + R::a_bytes;
+    uint64_t *grid = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + R::a_bytes + R::b_bytes + R::grid_bytes);
+    uint64_t *full_a = bars, *empty_a = bars + kMaxRing;                    // A producers <-> MMA, one pair per A stage
+    uint64_t *full_b = bars + 2 * kMaxRing, *empty_b = bars + 3 * kMaxRing;  // B producer(s) <-> MMA, one pair per B stage
+    uint64_t *acc_full = bars + 4 * kMaxRing;  // MMA -> epilogue, one per accumulator
     uint64_t *acc_empty = acc_full + 2;        // epilogue -> MMA
-    uint64_t *raw_full = bars + 20, *raw_empty = bars + 24;  // copy engine <-> unpacking warps, one pair per raw stage
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 28);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,12 +387,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         for (uint32_t a = 0; a < 2; a++) {
             mbar_init(&acc_full[a], 1);
             mbar_init(&acc_empty[a], 4);
-        }
-        if constexpr (RAW) {
-            for (uint32_t s = 0; s < kRawStages; s++) {
-                mbar_init(&raw_full[s], 1);
-                mbar_init(&raw_empty[s], kGroups * kAWarps);
-            }
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -392,7 +413,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         const uint32_t t = threadIdx.x % (kAWarps * 32);
         const uint32_t arow = t >> 1, ahalf = t & 1;  // thread t unpacks 32 weights of row arow
         uint32_t it0 = 0;  // stage counter at the start of the work item
-        [[maybe_unused]] uint32_t rit = 0;  // raw stages taken so far
         Work wk;
         // decoded values -> 16-bit floats -> this thread's four 16-byte chunks of stage s
         auto put = [&](const float (&v)[32], bool live, uint32_t it) -> bool {
@@ -406,9 +426,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 q[c4].w = live ? pack16<F16>(v[8 * c4 + 6], v[8 * c4 + 7]) : 0u;
             }
             if (use > 0 && !warp_wait(&empty_a[s], (use - 1) & 1, lane, abort_flag, p.status)) return false;
-            uint8_t *sa = a_ring + (size_t)s * kABytes;
+            const uint32_t sa = smem_u32(a_ring) + s * kABytes;
 #pragma unroll
-            for (int c4 = 0; c4 < 4; c4++) *reinterpret_cast<uint4 *>(sa + swz(arow, ahalf * 4 + c4)) = q[c4];
+            for (int c4 = 0; c4 < 4; c4++)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sa + swz(arow, ARaw<TY>::chunk(ahalf, c4))), "r"(q[c4].x),
+                             "r"(q[c4].y), "r"(q[c4].z), "r"(q[c4].w)
+                             : "memory");
             fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_a[s]);
@@ -418,35 +441,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             const uint32_t m0 = wk.mt * kBM;
             const uint32_t kb0 = wk.kb0, kb1 = wk.kb1;
             const bool arow_live = m0 + arow < p.m;
-            if constexpr (RAW) {
-                // one raw stage = block column jb = the k-blocks 4 jb .. 4 jb + 3 of the 128 rows; both
-                // groups wait for it, unpack their k-blocks out of it and hand it back
-                for (uint32_t jb = kb0 / kRawKBlocks; jb <= (kb1 - 1) / kRawKBlocks; jb++, rit++) {
-                    const uint32_t rs = rit % kRawStages;
-                    if (!warp_wait(&raw_full[rs], (rit / kRawStages) & 1, lane, abort_flag, p.status)) goto done;
-                    const uint8_t *blk = raw_ring + (size_t)rs * kRawBytes + arow * kRawBlock;
-                    const uint32_t lo = max(kb0, jb * kRawKBlocks), hi = min(kb1, (jb + 1) * kRawKBlocks);
-                    for (uint32_t kb = lo; kb < hi; kb++) {
-                        const uint32_t it = it0 + (kb - kb0);
-                        if (kGroups == 2 && (it & 1) != grp) continue;
-                        ARaw<TY> cur;
-                        cur.take(blk, kb, ahalf);
-                        float v[32];
-                        cur.decode(v, grid);
-                        if (!put(v, arow_live, it)) goto done;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&raw_empty[rs]);
+            const uint32_t wrow = min(m0 + arow, p.m - 1);
+            const uint8_t *wp = p.w + (size_t)wrow * p.row_bytes;
+            // this group's first k-block: the one whose stage counter has its parity
+            const uint32_t first = kb0 + (kGroups == 2 ? ((grp + it0) & 1) : 0);
+            // The bytes of the next k-block (Q4_K: of the next two) are fetched while this one is
+            // unpacked.  (Tried and slower: refilling a register set only after put(), whose proxy
+            // fence waits for the loads in flight; three sets taking turns without moves.)
+            if constexpr (ARaw<TY>::kAhead == 2) {
+                ARaw<TY> cur, n1, n2;
+                if (first < kb1) cur.load(wp, first, ahalf);
+                if (first + kGroups < kb1) n1.load(wp, first + kGroups, ahalf);
+                for (uint32_t kb = first; kb < kb1; kb += kGroups) {
+                    if (kb + 2 * kGroups < kb1) n2.load(wp, kb + 2 * kGroups, ahalf);
+                    float v[32];
+                    cur.decode(v, grid);
+                    if (!put(v, arow_live, it0 + (kb - kb0))) goto done;
+                    cur = n1;
+                    n1 = n2;
                 }
             } else {
-                const uint32_t wrow = min(m0 + arow, p.m - 1);
-                const uint8_t *wp = p.w + (size_t)wrow * p.row_bytes;
-                // this group's first k-block: the one whose stage counter has its parity
-                const uint32_t first = kb0 + (kGroups == 2 ? ((grp + it0) & 1) : 0);
                 ARaw<TY> cur, nxt;
                 if (first < kb1) cur.load(wp, first, ahalf);
                 for (uint32_t kb = first; kb < kb1; kb += kGroups) {
-                    if (kb + kGroups < kb1) nxt.load(wp, kb + kGroups, ahalf);
+                    if (kb + kGroups < kb1) nxt.load(wp, kb + kGroups, ahalf);  // lands while cur is unpacked
                     float v[32];
                     cur.decode(v, grid);
                     if (!put(v, arow_live, it0 + (kb - kb0))) goto done;
@@ -456,7 +474,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             it0 += kb1 - kb0;
         }
     } else if (warp == kTmaWarp) {
-        // ---------------- the copy engine's two clients, one thread each
+        // ---------------- one thread hands the B tiles to the copy engine
         if (ASYNC_B && lane == 0) {
             // B tiles of 16-bit activations: NACC x 256 tokens x 64 k per stage
             uint32_t it = 0;
@@ -465,7 +483,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 const uint32_t nblk = wk.ntok > kBN ? NACC : 1;
                 for (uint32_t kb = wk.kb0; kb < wk.kb1; kb++, it++) {
                     const uint32_t s = it % kBStages, use = it / kBStages;
-                    if (use > 0 && !mbar_wait(&empty_b[s], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
+                    if (use > 0 && !thread_wait(&empty_b[s], (use - 1) & 1, abort_flag, p.status)) {
                         // giving up: the copies already handed over land within microseconds;
                         // stay for a while so that they do not write into a CTA that has gone
                         const long long t0 = clock64();
@@ -476,22 +494,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     mbar_expect_tx(&full_b[s], nblk * kBBytes);
                     for (uint32_t a = 0; a < nblk; a++)
                         tma_load_tile(sb + a * kBBytes, &xmap, kb * kBK, wk.n0 + a * kBN, &full_b[s]);
-                }
-            }
-        } else if (RAW && lane == 1) {
-            // the weights as stored: block column jb of the item's 128 rows, rows past M as zeros
-            uint32_t rit = 0;
-            Work wk;
-            for (uint32_t j = 0; next_work<NACC>(p, j, wk); j++) {
-                for (uint32_t jb = wk.kb0 / kRawKBlocks; jb <= (wk.kb1 - 1) / kRawKBlocks; jb++, rit++) {
-                    const uint32_t rs = rit % kRawStages, use = rit / kRawStages;
-                    if (use > 0 && !mbar_wait(&raw_empty[rs], (use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
-                        const long long t0 = clock64();
-                        while (clock64() - t0 < 100000) {}
-                        goto done;
-                    }
-                    mbar_expect_tx(&raw_full[rs], kRawBytes);
-                    tma_load_tile(raw_ring + (size_t)rs * kRawBytes, &wmap, jb * kRawBlock, wk.mt * kBM, &raw_full[rs]);
                 }
             }
         }
@@ -568,14 +570,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 const uint32_t acc0 = NACC == 2 ? 0 : (tile & 1), acc_use = NACC == 2 ? tile : (tile >> 1);
                 bool ok = true;
                 for (uint32_t a = 0; a < (uint32_t)NACC && ok; a++)
-                    if (acc_use > 0) ok = mbar_wait(&acc_empty[acc0 + a], (acc_use - 1) & 1, abort_flag, p.status, kStatusGemmTimeout);
+                    if (acc_use > 0) ok = thread_wait(&acc_empty[acc0 + a], (acc_use - 1) & 1, abort_flag, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t kb0 = wk.kb0, kb1 = wk.kb1;
                 for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
                     const uint32_t s_a = it % kAStages, s_b = it % kBStages;
-                    if (!mbar_wait(&full_a[s_a], (it / kAStages) & 1, abort_flag, p.status, kStatusGemmTimeout) ||
-                        !mbar_wait(&full_b[s_b], (it / kBStages) & 1, abort_flag, p.status, kStatusGemmTimeout)) {
+                    if (!thread_wait(&full_a[s_a], (it / kAStages) & 1, abort_flag, p.status) ||
+                        !thread_wait(&full_b[s_b], (it / kBStages) & 1, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
@@ -744,11 +746,6 @@ static cudaError_t encode_map_2d(CUtensorMap *map, bool bytes, const void *base,
 static cudaError_t encode_x_map(CUtensorMap *map, const void *x, uint32_t k, uint32_t n) {
     return encode_map_2d(map, false, x, k, n, (uint64_t)k * 2, kBK, kBN, true);
 }
-// Q4_K weights W[m][row_bytes] as bytes: one 144-byte block x 128 rows per copy, as stored
-static cudaError_t encode_w_map(CUtensorMap *map, const void *w, uint32_t row_bytes, uint32_t m) {
-    return encode_map_2d(map, true, w, row_bytes, m, row_bytes, kRawBlock, kBM, false);
-}
-
 template <int TY, int XDT, typename OT, int NACC>
 static cudaError_t launch_n(const Args &a, const Outs &go, cudaStream_t s, int sms, int dev) {
     static bool attr_set[64] = {};  // the opt-in is per device
@@ -766,13 +763,7 @@ static cudaError_t launch_n(const Args &a, const Outs &go, cudaStream_t s, int s
         cudaError_t me = encode_x_map(&xmap, a.x, a.k, a.n);
         if (me != cudaSuccess) return me;
     }
-    alignas(64) CUtensorMap wmap;
-    memset(&wmap, 0, sizeof(wmap));
-    if constexpr (kRawByTma<TY>) {
-        cudaError_t me = encode_w_map(&wmap, a.w, a.row_bytes, a.m);
-        if (me != cudaSuccess) return me;
-    }
-    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, Rings<TY, NACC>::smem, s>>>(xmap, wmap, a, go);
+    gemm_tc_kernel<TY, XDT, OT, NACC><<<grid, kThreads, Rings<TY, NACC>::smem, s>>>(xmap, a, go);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || a.ksplit == 1) return e;
     const size_t count = (size_t)a.n * a.m;

@@ -30,6 +30,7 @@ def main():
     enc = CudaEnc(ctx)
     cases = [(GGUFType.Q4_K, 2560, 1024, 1), (GGUFType.Q4_K, 2560, 512, 1), (GGUFType.Q4_K, 1024, 256, 3),
              (GGUFType.IQ2_XXS, 5120, 512, 1), (GGUFType.Q8_0, 2048, 384, 2), (GGUFType.Q2_0, 2048, 640, 1),
+             (GGUFType.Q4_K, 9728, 640, 1), (GGUFType.IQ2_XXS, 17408, 512, 2),  # long rows, cut into k-chunks
              (GGUFType.Q4_K, 1024, 768, 40), (GGUFType.Q4_K, 8192, 256, 45)]  # more than 8 tokens: the matmul (one with k-ranges)
     # ordered: every launch waits for the exchange before it; free: nobody waits until gather_wait
     all_peers = [tp.PeerOutputs(ctx, [(n, m) for _, _, m, n in cases], free=f) for f in (False, True)]

@@ -631,3 +631,35 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
             assert np.isnan(o[n * m:]).all()
             ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
             assert rel_err(o[:n * m].reshape(n, m), ref) <= GEMV_TIGHT, (GGUFType(ty).name, k, m, n, xdt)
+
+
+@pytest.mark.parametrize("ty,k", [(GGUFType.Q4_K, 9728), (GGUFType.IQ2_XXS, 17408), (GGUFType.Q8_0, 8192),
+                                  (GGUFType.Q2_0, 24576)])
+@pytest.mark.parametrize("n", [1, 4])
+def test_long_rows_cut_into_k_chunks(ctx, ty, k, n):
+    """Rows too long for a ring stage are cut into k-chunks, one stage per (tile, chunk):
+    one tile, fewer tiles than SMs, more tiles than SMs; run twice; and two matrices in
+    one parallel region."""
+    enc = CudaEnc(ctx)
+    for m in (16, 200, 1600):
+        blocks = make_weights(ty, m, k, seed=m + k)
+        X = np.stack([lcg_fill(k, 11 + m + c) for c in range(n)])
+        ref = oracle.matmul(ty, blocks, k, m, X, n)
+        w = ctx.upload(blocks)
+        for rep in range(2):
+            out = torch.full((n, m), float("nan"), dtype=torch.float32, device="cuda")
+            enc.gemm(GGUFTensor("w", (k, m), ty), dev(X), out, w, n)
+            torch.cuda.synchronize()
+            assert rel_err(out.cpu().numpy(), ref) <= GEMV_TIGHT, (ty, k, m, n, rep)
+    ms = [208, 1000]
+    ws = [ctx.upload(make_weights(ty, m, k, seed=m)) for m in ms]
+    X = np.stack([lcg_fill(k, 3 + c) for c in range(n)])
+    got = [torch.full((n, m), float("nan"), dtype=torch.float32, device="cuda") for m in ms]
+    with enc.parallel():
+        for m, w, o in zip(ms, ws, got):
+            enc.gemm(GGUFTensor(f"w{m}", (k, m), ty), dev(X), o, w, n)
+    torch.cuda.synchronize()
+    for m, o in zip(ms, got):
+        ref = oracle.matmul(ty, make_weights(ty, m, k, seed=m), k, m, X, n)
+        assert rel_err(o.cpu().numpy(), ref) <= GEMV_TIGHT, (ty, k, m, n)
+    assert ctx.device_status() == 0
