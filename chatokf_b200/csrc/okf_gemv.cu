@@ -719,6 +719,86 @@ __device__ __forceinline__ void stage_x_bytes(uint32_t xs32, uint32_t es, const 
 template <int TY, int XDT>
 __device__ __forceinline__ void stage_x_wide(uint8_t *xs, float *xw, const GemvLayout &L, const void *x, uint32_t kdim,
                                              uint32_t u_first, uint32_t nu, uint32_t tid) {
+    if constexpr (TY != T_Q2_0) {
+        // An item is 8 consecutive k = the eight bytes thread c = item % 4 of a quad feeds into block
+        // item / 4; the 32 items of a (column, unit) pair are the lanes of one warp, so the unit's
+        // largest magnitude is one warp reduction and a block's sum two shuffles, as in the
+        // one-column panel.  The loads of four pairs go out before the first is worked on.
+        const uint32_t warp = tid >> 5, e8 = tid & 31, blk = e8 >> 2, c = e8 & 3;
+        const uint32_t pairs = L.nc * nu;
+        constexpr uint32_t kFlight = 4;
+        constexpr uint32_t kMagicBits = 0x4B400080u;  // 1.5 * 2^23 + 128 as a float
+        const uint32_t piece = xq_piece_offset(c, blk >> 1) + (blk & 1) * 8;
+        for (uint32_t base = warp; base < pairs; base += kFlight * kGemvWarps) {
+            XRaw8<XDT> raw[kFlight];
+            uint32_t col_of[kFlight], u_of[kFlight];
+#pragma unroll
+            for (uint32_t r = 0; r < kFlight; r++) {
+                const uint32_t pr = base + r * kGemvWarps;
+                const bool live = pr < pairs;
+                col_of[r] = live ? pr / nu : 0;
+                u_of[r] = live ? pr - col_of[r] * nu : 0;
+                const uint4 *src = reinterpret_cast<const uint4 *>(
+                    reinterpret_cast<const uint8_t *>(x) +
+                    ((size_t)col_of[r] * kdim + (size_t)(u_first + u_of[r]) * 256 + e8 * 8) * (XDT == DT_F32 ? 4 : 2));
+#pragma unroll
+                for (int j = 0; j < (XDT == DT_F32 ? 2 : 1); j++)
+                    raw[r].v[j] = live ? __ldg(src + j) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (uint32_t r = 0; r < kFlight; r++) {
+                if (base + r * kGemvWarps >= pairs) break;  // the same for the whole warp
+                float v[8];
+                if constexpr (XDT == DT_F32) {
+                    v[0] = __uint_as_float(raw[r].v[0].x); v[1] = __uint_as_float(raw[r].v[0].y);
+                    v[2] = __uint_as_float(raw[r].v[0].z); v[3] = __uint_as_float(raw[r].v[0].w);
+                    v[4] = __uint_as_float(raw[r].v[1].x); v[5] = __uint_as_float(raw[r].v[1].y);
+                    v[6] = __uint_as_float(raw[r].v[1].z); v[7] = __uint_as_float(raw[r].v[1].w);
+                } else {
+                    const uint32_t w[4] = {raw[r].v[0].x, raw[r].v[0].y, raw[r].v[0].z, raw[r].v[0].w};
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        if constexpr (XDT == DT_F16) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
+                            v[2 * e] = f.x; v[2 * e + 1] = f.y;
+                        } else {
+                            v[2 * e] = __uint_as_float(w[e] << 16);
+                            v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+                        }
+                    }
+                }
+                uint32_t mb = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) mb = max(mb, __float_as_uint(v[j]) & 0x7FFFFFFFu);
+                mb = __reduce_max_sync(0xffffffffu, mb);
+                const float amax = __uint_as_float(mb);
+                // as in the one-column panel: below 1e-30 the unit counts as zeros, an infinite
+                // amax gives inv = 0 and an infinite scale, a NaN gives inv = 0 and a NaN scale
+                const float inv = amax > 1e-30f ? __fdividef(kXqMax, amax) : 0.f;
+                const float scale = amax * (1.f / kXqMax);
+                uint32_t t[8], tsum = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    t[j] = __float_as_uint(fmaf(v[j], inv, __uint_as_float(kMagicBits)));
+                    tsum += t[j];
+                }
+                int qsum = (int)(tsum - 8u * kMagicBits);
+                qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+                qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+                uint8_t *dst = xs + (2 * col_of[r]) * L.es + u_of[r] * kXqUnit + piece;
+                *reinterpret_cast<uint2 *>(dst) =
+                    make_uint2(prmt(prmt(t[0], t[1], 0x0051u), prmt(t[2], t[3], 0x0051u), 0x5410u),
+                               prmt(prmt(t[4], t[5], 0x0051u), prmt(t[6], t[7], 0x0051u), 0x5410u));
+                *reinterpret_cast<uint2 *>(dst + L.es) =
+                    make_uint2(prmt(prmt(t[0], t[1], 0x0040u), prmt(t[2], t[3], 0x0040u), 0x5410u) ^ 0x80808080u,
+                               prmt(prmt(t[4], t[5], 0x0040u), prmt(t[6], t[7], 0x0040u), 0x5410u) ^ 0x80808080u);
+                float *w12 = xw + ((size_t)u_of[r] * 4 + col_of[r]) * 12;
+                if (c == 0) reinterpret_cast<int *>(w12)[4 + blk] = qsum;
+                if (e8 == 0) w12[0] = scale;
+            }
+        }
+        return;
+    }
     const uint32_t items_per_col = nu * 16;
     const uint32_t total = (L.nc * items_per_col + 31) & ~31u;
     constexpr uint32_t kFlight = 3;  // items a thread has in flight: the loads go out first
@@ -1161,11 +1241,10 @@ __global__ void __launch_bounds__(kGemvThreadsMax, OKF_GEMV_MINB) gemv_kernel(Ge
 constexpr uint32_t kSharedBudget = 112 * 1024;
 
 static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, uint32_t tab_copies,
-                             GemvArgs &a, GemvLayout &L) {
+                             uint32_t budget, GemvArgs &a, GemvLayout &L) {
     const uint32_t ub = ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
     L.nc = sep ? 1 : n;
     L.ecols = sep ? 2 : 2 * n;
-    const uint32_t budget = kSharedBudget;
     const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
     L.group = 8192 / per_tile;
     if (L.group < 1) L.group = 1;
@@ -1254,21 +1333,29 @@ static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint3
 
 // IQ2_XXS: as many side-by-side copies of the codebook as leave room for a plan that
 // keeps all of x resident (16 copies make every look-up free of bank conflicts).
-static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, GemvArgs &a,
-                        GemvLayout &L) {
-    if (ty != T_IQ2_XXS) return gemv_layout_with(ty, nunit, n, sep, tiles_per_cta, 1, a, L);
+static bool gemv_layout_in(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, uint32_t budget,
+                           GemvArgs &a, GemvLayout &L) {
+    if (ty != T_IQ2_XXS) return gemv_layout_with(ty, nunit, n, sep, tiles_per_cta, 1, budget, a, L);
     GemvArgs fa = a;
     GemvLayout fl = L;
     bool have = false;
     for (uint32_t copies = 16; copies >= 1; copies /= 2) {
         GemvArgs ta = a;
         GemvLayout tl = L;
-        if (!gemv_layout_with(ty, nunit, n, sep, tiles_per_cta, copies, ta, tl)) continue;
+        if (!gemv_layout_with(ty, nunit, n, sep, tiles_per_cta, copies, budget, ta, tl)) continue;
         if (tl.panel == ta.nchunk) { a = ta; L = tl; return true; }
         if (!have) { fa = ta; fl = tl; have = true; }
     }
     if (have) { a = fa; L = fl; }
     return have;
+}
+
+static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, GemvArgs &a,
+                        GemvLayout &L) {
+    // (Tried for several columns of long rows, whose panel of x does not fit beside the ring in
+    // half an SM's shared memory: taking the SM alone with the whole panel resident.  Slower:
+    // the next kernel can then not prefetch under this one.)
+    return gemv_layout_in(ty, nunit, n, sep, tiles_per_cta, kSharedBudget, a, L);
 }
 
 template <int TY, int XDT, bool SEP>
