@@ -1358,10 +1358,22 @@ static bool gemv_layout(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t t
     return gemv_layout_in(ty, nunit, n, sep, tiles_per_cta, kSharedBudget, a, L);
 }
 
+// CTAs of a launch: one per SM, each with its share of the tiles -- except when there are only
+// a few more tiles than SMs (160 on 148): then two tiles in a row on a dozen SMs would set the
+// launch's time, and one CTA per tile is used instead; an SM has room for two of them side by
+// side, and they do not slow each other down much (a CTA alone issues on a third of the cycles).
+// (One column only: with several columns two CTAs on an SM, each staging its slices of x at
+// barriers, were 16 % slower than two tiles in a row.)
+static uint32_t gemv_ctas(uint32_t tiles, int sms, bool sep) {
+    const uint32_t n = (uint32_t)sms;
+    if (tiles <= n) return tiles;
+    return sep && tiles <= n + n / 4 ? tiles : n;
+}
+
 template <int TY, int XDT, bool SEP>
 static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int sms, int dev) {
     GemvLayout L;
-    const uint32_t ctas = a.tiles < (uint32_t)sms ? a.tiles : (uint32_t)sms;
+    const uint32_t ctas = gemv_ctas(a.tiles, sms, SEP);
     if (!gemv_layout(TY, a.nunit, a.n, SEP, (a.tiles + ctas - 1) / ctas, a, L)) return cudaErrorInvalidConfiguration;
     static bool attr_set[64] = {};  // the opt-in is per device
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
@@ -1414,10 +1426,9 @@ bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, 
     }
     GemvArgs a = {};
     GemvLayout L;
-    const uint32_t ctas = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    const uint32_t tpc = (tiles + ctas - 1) / ctas;
-    if (!gemv_layout(ty, k / 256, 1, true, tpc, a, L)) return false;
-    if (n > 1 && !gemv_layout(ty, k / 256, n < 4 ? n : 4, false, tpc, a, L)) return false;
+    const uint32_t ctas = gemv_ctas(tiles, sms, true), ctas_wide = gemv_ctas(tiles, sms, false);
+    if (!gemv_layout(ty, k / 256, 1, true, (tiles + ctas - 1) / ctas, a, L)) return false;
+    if (n > 1 && !gemv_layout(ty, k / 256, n < 4 ? n : 4, false, (tiles + ctas_wide - 1) / ctas_wide, a, L)) return false;
     return true;
 }
 
