@@ -60,6 +60,9 @@ WORKLOADS = {
                                ("v", GGUFType.IQ2_XXS, 5120, 1024), ("o", GGUFType.IQ2_XXS, 5120, 5120),
                                ("gate", GGUFType.IQ2_XXS, 5120, 17408), ("up", GGUFType.IQ2_XXS, 5120, 17408),
                                ("down", GGUFType.IQ2_XXS, 17408, 5120)], 64),
+    # not a BASELINE configuration: the headline's shapes in the gemma trunks' Q4_0
+    "q4_0_ffn_gemv": (5, F16, [("gate", GGUFType.Q4_0, 2560, 9728), ("up", GGUFType.Q4_0, 2560, 9728),
+                                ("down", GGUFType.Q4_0, 9728, 2560)], 64),
 }
 HEADLINE = "q4k_ffn_gemv"
 
@@ -750,7 +753,8 @@ def run_ours(args):
             plan = [("q8_0_gemv_2048", 1, {}), ("ternary_ffn", 1, {}), ("iq2xxs_trunk", 1, {}),
                     ("iq2xxs_trunk", 4, {}), ("q4k_ffn_gemv", 4, {}), ("q4k_ffn_gemv", 8, {}),
                     ("q4k_prefill", 32, {"steps": 5}), ("q4k_prefill", 128, {"steps": 5}),
-                    ("q4k_prefill", 512, {"steps": 5}), ("ternary_ffn", 512, {"steps": 5, "layers": 4})]
+                    ("q4k_prefill", 512, {"steps": 5}), ("ternary_ffn", 512, {"steps": 5, "layers": 4}),
+                    ("q4_0_ffn_gemv", 1, {}), ("q4_0_ffn_gemv", 4, {})]
         else:
             # the configurations that are specified as row-sharded: the IQ2_XXS trunk at batch 1 and 4
             # and the 512-token matmul with the stores into every rank's output fused into its

@@ -851,7 +851,7 @@ uint32_t gemm_tc_ksplit(uint32_t k, uint32_t m, uint32_t n, int xdt, int sms) {
 }
 
 bool gemm_tc_supported(int ty, uint32_t k, uint32_t m, const void *w, const void *x, int xdt, uint32_t n) {
-    if (ty != T_Q4_K && ty != T_Q8_0 && ty != T_Q2_0 && ty != T_IQ2_XXS) return false;
+    if (!has_fast_kernels(ty)) return false;
     if (k % 64 || m == 0 || n == 0) return false;
     if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
     if (ty == T_Q4_K && (uintptr_t)w % 16) return false;
@@ -884,6 +884,7 @@ cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, con
     switch (ty) {
     case T_Q4_K: return tc::launch_x<T_Q4_K>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     case T_Q8_0: return tc::launch_x<T_Q8_0>(a, go, plan.nacc, xdt, odt, s, sms, dev);
+    case T_Q4_0: return tc::launch_x<T_Q4_0>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     case T_Q2_0: return tc::launch_x<T_Q2_0>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     case T_IQ2_XXS: return tc::launch_x<T_IQ2_XXS>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     default: return cudaErrorInvalidValue;

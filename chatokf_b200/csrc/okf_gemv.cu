@@ -39,6 +39,7 @@ namespace okf {
 template <int TY> struct UnitGeom;
 template <> struct UnitGeom<T_Q4_K> { static constexpr uint32_t bytes = 144; };
 template <> struct UnitGeom<T_Q8_0> { static constexpr uint32_t bytes = 272; };
+template <> struct UnitGeom<T_Q4_0> { static constexpr uint32_t bytes = 144; };
 template <> struct UnitGeom<T_Q2_0> { static constexpr uint32_t bytes = 68; };
 template <> struct UnitGeom<T_IQ2_XXS> { static constexpr uint32_t bytes = 66; };
 
@@ -247,6 +248,8 @@ __device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_
         k.m2 = k.low ? 0u : 0x30303030u;
     } else if constexpr (TY == T_Q8_0) {
         k.qoff = 68 * c;
+    } else if constexpr (TY == T_Q4_0) {
+        k.qoff = 36 * c;
     } else if constexpr (TY == T_Q2_0) {
         k.hoff = 34 * (c >> 1);
         k.qoff = k.hoff + 2 + 16 * (c & 1);
@@ -317,6 +320,44 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
                   fa.y * (byte_to_f32(mn, 0) * x0 + byte_to_f32(mn, 1) * x1);
         acc[1] += fb.x * (byte_to_f32(sc, 2) * (xs * lb) + byte_to_f32(sc, 3) * (xs16 * hb_)) -
                   fb.y * (byte_to_f32(mn, 2) * x0 + byte_to_f32(mn, 3) * x1);
+    } else if constexpr (TY == T_Q4_0) {
+        // eight blocks {f16 d; u8 qs[16]}, byte j = weights j (low nibble) and j + 16 (high), value
+        // (q - 8) * d (LLM/Gemma/Gemma4Quant.swift:30-49).  Thread c takes blocks 2c and 2c+1:
+        // {d0, qs0[16], d1, qs1[16]} = 9 words (units start on 16-byte boundaries, 36c is a
+        // multiple of 4).  Nibbles are masked in place; the high ones stay 16 x the value.
+        uint32_t wa[9], wb[9];
+#pragma unroll
+        for (int i = 0; i < 9; i++) {
+            wa[i] = lds32(ua + K.qoff + 4 * i);
+            wb[i] = lds32(ub + K.qoff + 4 * i);
+        }
+        uint32_t qa[8], qb[8];  // block 0's bytes start two bytes into word 0, block 1's on word 5
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            qa[i] = __funnelshift_r(wa[i], wa[i + 1], 16);
+            qb[i] = __funnelshift_r(wb[i], wb[i + 1], 16);
+            qa[4 + i] = wa[5 + i];
+            qb[4 + i] = wb[5 + i];
+        }
+        const uint32_t ml = 0x0F0F0F0Fu, mh = 0xF0F0F0F0u;
+        float part[2][2];  // [block][row]: sum of q * x in units of x's scale
+#pragma unroll
+        for (int blk = 0; blk < 2; blk++) {
+            const uint32_t *a = qa + 4 * blk, *b = qb + 4 * blk;
+            const uint32_t *xb = xf + 8 * blk;  // bytes of k 0..15 (low nibbles), then 16..31 (high)
+            int lo[4], hi[4];
+            imma0<false>(lo, a[0] & ml, b[0] & ml, a[1] & ml, b[1] & ml, xb[0], xb[1]);
+            imma0<false>(hi, a[0] & mh, b[0] & mh, a[1] & mh, b[1] & mh, xb[4], xb[5]);
+            imma<false>(lo, a[2] & ml, b[2] & ml, a[3] & ml, b[3] & ml, xb[2], xb[3]);
+            imma<false>(hi, a[2] & mh, b[2] & mh, a[3] & mh, b[3] & mh, xb[6], xb[7]);
+            part[blk][0] = fmaf(join_hi_lo(hi[0], hi[1]), 0.0625f, join_hi_lo(lo[0], lo[1]));
+            part[blk][1] = fmaf(join_hi_lo(hi[2], hi[3]), 0.0625f, join_hi_lo(lo[2], lo[3]));
+        }
+        const float x0 = __uint_as_float(xi.y), x1 = __uint_as_float(xi.z);  // scale * sum of x per block
+        const float da0 = f16bits(wa[0] & 0xFFFF), da1 = f16bits(wa[4] >> 16);
+        const float db0 = f16bits(wb[0] & 0xFFFF), db1 = f16bits(wb[4] >> 16);
+        acc[0] += da0 * fmaf(xs, part[0][0], -8.f * x0) + da1 * fmaf(xs, part[1][0], -8.f * x1);
+        acc[1] += db0 * fmaf(xs, part[0][1], -8.f * x0) + db1 * fmaf(xs, part[1][1], -8.f * x1);
     } else if constexpr (TY == T_Q8_0) {
         // eight blocks {f16 d; i8 q[32]} (LLM/Gemma/Gemma4Quant.swift:51-69); thread c
         // takes blocks 2c and 2c+1: {d0, q0[32], d1, q1[32]} = 17 words (units start on
@@ -470,6 +511,25 @@ __device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, 
         auto join = [](int hi, int lo) { return fmaf((float)hi, 256.f, (float)lo); };
         acc[0] += xs * (da * (join(te[0], te[1]) + join(to[0] >> 4, to[1] >> 4)) - dma * (float)mina);
         acc[1] += xs * (db * (join(te[2], te[3]) + join(to[2] >> 4, to[3] >> 4)) - dmb * (float)minb);
+    } else if constexpr (TY == T_Q4_0) {
+        const int4 x03 = *reinterpret_cast<const int4 *>(xw + 4), x47 = *reinterpret_cast<const int4 *>(xw + 8);
+        const int xb[8] = {x03.x, x03.y, x03.z, x03.w, x47.x, x47.y, x47.z, x47.w};
+        float fa = 0.f, fb = 0.f;
+        const uint32_t sh = 4 * (c >> 1);  // threads 0, 1: low nibbles (k 0..15); 2, 3: high (k 16..31)
+#pragma unroll
+        for (int b = 0; b < 8; b++) {  // block b: {f16 d; u8 qs[16]}, this thread's eight bytes at 2 + 8 (c & 1)
+            uint32_t qa[2], qb[2];
+            lds_a2<2>(ua + 18 * b + 2 + 8 * (c & 1), qa);
+            lds_a2<2>(ub + 18 * b + 2 + 8 * (c & 1), qb);
+            int d[4];
+            imma0<false>(d, (qa[0] >> sh) & 0x0F0F0F0Fu, (qb[0] >> sh) & 0x0F0F0F0Fu, (qa[1] >> sh) & 0x0F0F0F0Fu,
+                         (qb[1] >> sh) & 0x0F0F0F0Fu, xf[2 * b], xf[2 * b + 1]);
+            // (q - 8) * d: eight times the block's sum of x leaves again
+            fa += f16bits(ld_u16(ua + 18 * b)) * (float)(d[0] * 256 + d[1] - 8 * xb[b]);
+            fb += f16bits(ld_u16(ub + 18 * b)) * (float)(d[2] * 256 + d[3] - 8 * xb[b]);
+        }
+        acc[0] += xs * fa;
+        acc[1] += xs * fb;
     } else if constexpr (TY == T_Q8_0) {
         float fa = 0.f, fb = 0.f;
 #pragma unroll
@@ -1242,7 +1302,7 @@ constexpr uint32_t kSharedBudget = 112 * 1024;
 
 static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, uint32_t tab_copies,
                              uint32_t budget, GemvArgs &a, GemvLayout &L) {
-    const uint32_t ub = ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
+    const uint32_t ub = (ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
     L.nc = sep ? 1 : n;
     L.ecols = sep ? 2 : 2 * n;
     const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
@@ -1415,7 +1475,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
 
 bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
                           const void *x, int xdt, uint32_t n, int sms) {
-    if (ty != T_Q4_K && ty != T_Q8_0 && ty != T_Q2_0 && ty != T_IQ2_XXS) return false;
+    if (!has_fast_kernels(ty)) return false;
     if (nseg == 0 || nseg > (uint32_t)kGemvSegs || n == 0 || n > 8) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
     if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
@@ -1448,7 +1508,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
     GemvArgs a = {};
     a.status = status; a.k = k;
     a.nunit = k / 256;
-    a.row_bytes = a.nunit * (ty == T_Q4_K ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66);
+    a.row_bytes = a.nunit * ((ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66);
     uint32_t tiles = 0;
     for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {
         const uint32_t j = i < nseg ? i : nseg - 1;  // unused slots repeat the last one
@@ -1490,6 +1550,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         switch (ty) {
         case T_Q4_K: e = launch_ty<T_Q4_K>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q8_0: e = launch_ty<T_Q8_0>(a, G, xdt, sep, s, sms, dev); break;
+        case T_Q4_0: e = launch_ty<T_Q4_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q2_0: e = launch_ty<T_Q2_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_IQ2_XXS: e = launch_ty<T_IQ2_XXS>(a, G, xdt, sep, s, sms, dev); break;
         default: e = cudaErrorInvalidValue;

@@ -39,12 +39,12 @@ typedef enum okf_type {
     OKF_Q4_K = 12,    /* 144 B / 256 weights */
     OKF_IQ2_XXS = 16, /* 66 B / 256 weights  */
     OKF_Q2_0 = 42,    /* 34 B / 128 weights, ternary */
+    OKF_Q4_0 = 2,     /* 18 B / 32 weights (gemma trunks; Gemma/Gemma4Quant.swift:30-49) */
     /* The rest of the decoder table the trunks' files mix in (Blocks.decoder,
      * Quantize/Blocks.swift:10-29; Gemma/Gemma4Quant.swift:5-49): the same entry
      * points take them, bit-exact decode included, on the plain warp-per-row /
      * fp32-tile kernels (counted by okf_fallback_count), not on the streaming
      * integer-MMA matvec or the tensor-core tile. */
-    OKF_Q4_0 = 2,     /* 18 B / 32 weights   */
     OKF_Q5_K = 13,    /* 176 B / 256 weights */
     OKF_Q6_K = 14,    /* 210 B / 256 weights */
     OKF_IQ4_NL = 20   /* 18 B / 32 weights, codebook of 16 values */
