@@ -471,8 +471,9 @@ def e2e_steps(ctx, L, steps, warmup, torch, dist):
     xd = {k: torch.empty(L.n, k, dtype=torch.float32, device="cuda") for k in L.xs}
     h2d = sum(L.n * t.K * 4 for t, _, _, _ in L.items)
     d2h = sum(L.n * t.M * 4 * L.world for t, _, _, _ in L.items)
+    host_calls = [(t, w, hx[t.K].data_ptr(), hy[t.M].data_ptr()) for t, w, _, _ in L.items]
     if L.world == 1:
-        api = "okf_matmul_host (QB.matvec twin), one synchronous call per matrix"
+        api = "okf_matmul_host (QB.matvec twin) on page-locked host buffers, one synchronous call per matrix"
     elif L.gather == "fused":
         api = ("per matrix: cudaMemcpyAsync of x, okf_gemm_gather (rows stored into every rank's output by the "
                "kernel), okf_gather_wait, okf_copy_to_host of the whole y")
@@ -480,10 +481,12 @@ def e2e_steps(ctx, L, steps, warmup, torch, dist):
         api = "per matrix: copy of x, okf_gemm on this rank's rows, NCCL all-gather, copy of the whole y, stream sync"
 
     def one():
+        if L.world == 1:
+            for t, w, x_addr, y_addr in host_calls:
+                qb.matmul_at(t, w, x_addr, L.n, y_addr)
+            return
         for idx, (t, w, _, out) in enumerate(L.items):
-            if L.world == 1:
-                qb.matmul(t, w, hx[t.K].numpy(), L.n, hy[t.M].numpy())
-            elif L.gather == "fused":
+            if L.gather == "fused":
                 xd[t.K].copy_(hx[t.K], non_blocking=True)
                 enc.gemm_gather(t, xd[t.K], L.peers.slot(idx, t.M), w, L.n)
                 enc.gather_wait()

@@ -290,6 +290,14 @@ class QB:
                                        X.ctypes.data, int(N), out.ctypes.data), "okf_matmul_host")
         return out
 
+    def matmul_at(self, w: GGUFTensor, off: Weights, x_addr: int, N: int, out_addr: int) -> None:
+        """okf_matmul_host on raw host addresses (N x K floats in, N x M floats out), as a host
+        that keeps its own buffers calls it: nothing is checked, converted or allocated here."""
+        c = self.ctx
+        rc = c.lib.okf_matmul_host(c.h, int(w.type), off.h, w.offset, w.K, w.M, x_addr, N, out_addr)
+        if rc:
+            c._check(rc, "okf_matmul_host")
+
     def dequant(self, w: GGUFTensor, off: Weights, row: int, count: int) -> np.ndarray:
         """QB.dequant(w, row:, count:, into:): `count` weights from the row start."""
         out = np.empty(count, dtype=np.float32)
