@@ -692,3 +692,37 @@ def test_q4_0_streaming_matvec_and_tile(ctx, xdt):
             tol = gemm_tol(xdt, F32) if n > 8 and fast else GEMV_TIGHT
             assert rel_err(o[:n * m].reshape(n, m), ref) <= tol, (k, m, n, xdt)
     assert ctx.device_status() == 0
+
+
+def test_host_operator_called_again_and_again_with_the_same_buffers(ctx):
+    """A decode loop calls the host-buffer operator with the same tensor and the same
+    page-locked buffers for every token, only x's contents change: every call has to give
+    that call's result (the copy of x and the kernel may be replayed from a recorded graph),
+    the launch counter has to count every call, and more buffer sets than a cache could hold
+    must still be served."""
+    qb = QB(ctx)
+    ty, k, m = GGUFType.Q4_K, 2048, 200
+    blocks = make_weights(ty, m, k, seed=5)
+    w = ctx.upload(blocks)
+    t = GGUFTensor("w", (k, m), ty)
+    sets = [(torch.empty(k, dtype=torch.float32).pin_memory(), torch.empty(m, dtype=torch.float32).pin_memory())
+            for _ in range(11)]
+    for rep in range(3):
+        for i, (hx, hy) in enumerate(sets):
+            x = lcg_fill(k, 40 + 7 * rep + i)
+            hx.copy_(torch.from_numpy(x))
+            hy.fill_(float("nan"))
+            before = ctx.launches
+            qb.matmul_at(t, w, hx.data_ptr(), 1, hy.data_ptr())
+            assert ctx.launches == before + 1
+            assert rel_err(hy.numpy(), oracle.matvec(ty, blocks, k, m, x)) <= GEMV_TIGHT, (rep, i)
+    # the same buffers, other shapes and another tensor
+    ty2, m2 = GGUFType.Q8_0, 64
+    blocks2 = make_weights(ty2, m2, k, seed=6)
+    w2 = ctx.upload(blocks2)
+    hx, hy = sets[0]
+    x = lcg_fill(k, 99)
+    hx.copy_(torch.from_numpy(x))
+    qb.matmul_at(GGUFTensor("w2", (k, m2), ty2), w2, hx.data_ptr(), 1, hy.data_ptr())
+    assert rel_err(hy.numpy()[:m2], oracle.matvec(ty2, blocks2, k, m2, x)) <= GEMV_TIGHT
+    assert ctx.device_status() == 0
