@@ -40,6 +40,7 @@ template <int TY> struct UnitGeom;
 template <> struct UnitGeom<T_Q4_K> { static constexpr uint32_t bytes = 144; };
 template <> struct UnitGeom<T_Q8_0> { static constexpr uint32_t bytes = 272; };
 template <> struct UnitGeom<T_Q4_0> { static constexpr uint32_t bytes = 144; };
+template <> struct UnitGeom<T_Q6_K> { static constexpr uint32_t bytes = 210; };
 template <> struct UnitGeom<T_Q2_0> { static constexpr uint32_t bytes = 68; };
 template <> struct UnitGeom<T_IQ2_XXS> { static constexpr uint32_t bytes = 66; };
 
@@ -250,6 +251,11 @@ __device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_
         k.qoff = 68 * c;
     } else if constexpr (TY == T_Q4_0) {
         k.qoff = 36 * c;
+    } else if constexpr (TY == T_Q6_K) {
+        k.qoff = 64 * (c >> 1);         // ql of this half of the block
+        k.hoff = 128 + 32 * (c >> 1);   // qh of this half
+        k.sel = 4 * (c & 1);            // low or high nibbles of ql; bits 0-3 or 4-7 of qh
+        k.m1 = 192 + 4 * c;             // this quarter's four scales
     } else if constexpr (TY == T_Q2_0) {
         k.hoff = 34 * (c >> 1);
         k.qoff = k.hoff + 2 + 16 * (c & 1);
@@ -358,6 +364,46 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
         const float db0 = f16bits(wb[0] & 0xFFFF), db1 = f16bits(wb[4] >> 16);
         acc[0] += da0 * fmaf(xs, part[0][0], -8.f * x0) + da1 * fmaf(xs, part[1][0], -8.f * x1);
         acc[1] += db0 * fmaf(xs, part[0][1], -8.f * x0) + db1 * fmaf(xs, part[1][1], -8.f * x1);
+    } else if constexpr (TY == T_Q6_K) {
+        // {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d} (LLM/Quantize/KQuants.swift:160-177): weight =
+        // d * scale[group of 16] * (q - 32), q = four bits of ql and two of qh.  Quarter c is
+        // elements 64c .. 64c + 63 = the low (c even) or high (c odd) nibbles of the 64 ql bytes of
+        // half c / 2, with qh bits 4(c & 1) .. +1 for its first 32 elements and the next two bits
+        // for the other 32, and scales 4c .. 4c + 3.  q - 32 is made a signed byte in place
+        // (flip bit 5, then copy it into bits 6 and 7: 0x20 * 6 = 0xC0 stays inside the byte), so
+        // the signed MMA needs no correction; one accumulator per 16-wide scale group.
+        // Units are only 2-byte aligned.
+        uint32_t sa[1], sb[1];
+        lds_a2<1>(ua + K.m1, sa);
+        lds_a2<1>(ub + K.m1, sb);
+        const float da = f16bits(lds16(ua + 208)), db = f16bits(lds16(ub + 208));
+        const uint32_t sh = K.sel;
+        float suma = 0.f, sumb = 0.f;
+#pragma unroll
+        for (int grp = 0; grp < 4; grp++) {  // 16 elements: 16 bytes of ql, 16 of qh (groups 2, 3 reuse those of 0, 1)
+            uint32_t la[4], lb[4], ha[4], hb[4];
+            lds_a2<4>(ua + K.qoff + 16 * grp, la);
+            lds_a2<4>(ub + K.qoff + 16 * grp, lb);
+            lds_a2<4>(ua + K.hoff + 16 * (grp & 1), ha);
+            lds_a2<4>(ub + K.hoff + 16 * (grp & 1), hb);
+            const uint32_t hs = sh + 2 * (grp >> 1);
+            uint32_t qa[4], qb[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t va = (((la[i] >> sh) & 0x0F0F0F0Fu) | (((ha[i] >> hs) & 0x03030303u) << 4)) ^ 0x20202020u;
+                const uint32_t vb = (((lb[i] >> sh) & 0x0F0F0F0Fu) | (((hb[i] >> hs) & 0x03030303u) << 4)) ^ 0x20202020u;
+                qa[i] = va | ((va & 0x20202020u) * 6u);
+                qb[i] = vb | ((vb & 0x20202020u) * 6u);
+            }
+            int d[4];
+            imma0<true>(d, qa[0], qb[0], qa[1], qb[1], xf[4 * grp], xf[4 * grp + 1]);
+            imma<true>(d, qa[2], qb[2], qa[3], qb[3], xf[4 * grp + 2], xf[4 * grp + 3]);
+            const float fa = (float)((int)(sa[0] << (24 - 8 * grp)) >> 24), fb = (float)((int)(sb[0] << (24 - 8 * grp)) >> 24);
+            suma = fmaf(fa, join_hi_lo(d[0], d[1]), suma);
+            sumb = fmaf(fb, join_hi_lo(d[2], d[3]), sumb);
+        }
+        acc[0] += (da * xs) * suma;
+        acc[1] += (db * xs) * sumb;
     } else if constexpr (TY == T_Q8_0) {
         // eight blocks {f16 d; i8 q[32]} (LLM/Gemma/Gemma4Quant.swift:51-69); thread c
         // takes blocks 2c and 2c+1: {d0, q0[32], d1, q1[32]} = 17 words (units start on
@@ -1302,7 +1348,7 @@ constexpr uint32_t kSharedBudget = 112 * 1024;
 
 static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, uint32_t tab_copies,
                              uint32_t budget, GemvArgs &a, GemvLayout &L) {
-    const uint32_t ub = (ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66;
+    const uint32_t ub = (ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : 66;
     L.nc = sep ? 1 : n;
     L.ecols = sep ? 2 : 2 * n;
     const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
@@ -1344,7 +1390,7 @@ static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint3
             const uint32_t seg = cb * ub;
             L.ragged = (row_bytes % 16 || seg % 16) ? 1 : 0;
             // Q4_K reads its blocks with 16-byte loads, and its rows are always aligned
-            if (L.ragged && ty != T_IQ2_XXS && ty != T_Q2_0) continue;
+            if (L.ragged && ty != T_IQ2_XXS && ty != T_Q2_0 && ty != T_Q6_K) continue;
             rs = L.ragged ? ((seg + 15 + 15) & ~15u) : seg;  // room for the skipped bytes and the round-up
             if (rs % 32 != 16) rs += 16;                      // rows g and g + 1 on different banks
             stage = 16 * rs;
@@ -1457,13 +1503,16 @@ static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int
 
 template <int TY>
 static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bool sep, cudaStream_t s, int sms, int dev) {
+    if constexpr (TY == T_Q6_K) {
+        if (!sep) return cudaErrorInvalidValue;  // no several-column kernel for this type
+    }
     if (sep) {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, true>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, true>(a, G, s, sms, dev);
         case DT_F32: return launch_t<TY, DT_F32, true>(a, G, s, sms, dev);
         }
-    } else {
+    } else if constexpr (TY != T_Q6_K) {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, false>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, false>(a, G, s, sms, dev);
@@ -1476,6 +1525,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
 bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
                           const void *x, int xdt, uint32_t n, int sms) {
     if (!has_fast_kernels(ty)) return false;
+    if (ty == T_Q6_K && n > 1) return false;  // one column only: wider requests take the plain kernel
     if (nseg == 0 || nseg > (uint32_t)kGemvSegs || n == 0 || n > 8) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
     if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
@@ -1508,7 +1558,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
     GemvArgs a = {};
     a.status = status; a.k = k;
     a.nunit = k / 256;
-    a.row_bytes = a.nunit * ((ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : 66);
+    a.row_bytes = a.nunit * ((ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : 66);
     uint32_t tiles = 0;
     for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {
         const uint32_t j = i < nseg ? i : nseg - 1;  // unused slots repeat the last one
@@ -1551,6 +1601,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         case T_Q4_K: e = launch_ty<T_Q4_K>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q8_0: e = launch_ty<T_Q8_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q4_0: e = launch_ty<T_Q4_0>(a, G, xdt, sep, s, sms, dev); break;
+        case T_Q6_K: e = launch_ty<T_Q6_K>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q2_0: e = launch_ty<T_Q2_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_IQ2_XXS: e = launch_ty<T_IQ2_XXS>(a, G, xdt, sep, s, sms, dev); break;
         default: e = cudaErrorInvalidValue;

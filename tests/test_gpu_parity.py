@@ -611,7 +611,8 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
     LLM/Gemma/Gemma4Quant.swift:93-114): the committed fixture, then 1, 4 and 33 columns
     against the oracle.  IQ4_NL, Q5_K and Q6_K run on the warp-per-row / fp32-tile kernels
     with exact decode, so the matvec bound applies at every width, and each call is counted
-    as a fallback; Q4_0 has the streaming matvec and the tensor-core tile."""
+    as a fallback; Q4_0 has the streaming matvec and the tensor-core tile, Q6_K the one-column
+    matvec and the tile."""
     g = golden(ty)
     k, m = int(g["k"]), int(g["m"])
     got = QB(ctx).matvec(GGUFTensor("w", (k, m), ty), ctx.upload(g["blocks"]), g["x"])
@@ -626,7 +627,7 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
             out = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
             enc.gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
             torch.cuda.synchronize()
-            fast = ty == GGUFType.Q4_0
+            fast = ty == GGUFType.Q4_0 or (ty == GGUFType.Q6_K and (n == 1 or n > 8))
             assert ctx.fallbacks == before + (0 if fast else 1)
             o = out.cpu().numpy()
             assert np.isnan(o[n * m:]).all()
@@ -725,4 +726,32 @@ def test_host_operator_called_again_and_again_with_the_same_buffers(ctx):
     hx.copy_(torch.from_numpy(x))
     qb.matmul_at(GGUFTensor("w2", (k, m2), ty2), w2, hx.data_ptr(), 1, hy.data_ptr())
     assert rel_err(hy.numpy()[:m2], oracle.matvec(ty2, blocks2, k, m2, x)) <= GEMV_TIGHT
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("xdt", [F32, F16, BF16])
+def test_q6_k_one_column_matvec_and_tile(ctx, xdt):
+    """Q6_K (the output projection of mixed K-quant files; KQuant.q6K,
+    LLM/Quantize/KQuants.swift:160-177) through the integer-MMA matvec at one column and the
+    tensor-core tile above eight, against the oracle; blocks of 210 bytes leave rows and units
+    only 2-byte aligned, K short and long enough to be cut into k-chunks.  Two to eight
+    columns take the plain kernel."""
+    enc = CudaEnc(ctx)
+    ty = GGUFType.Q6_K
+    for k, m in [(256, 16), (256, 37), (2560, 300), (5120, 1000), (9728, 205), (17408, 64)]:
+        blocks = make_weights(ty, m, k, seed=k + m)
+        w = ctx.upload(blocks)
+        for n in (1, 3, 40):
+            X = np.stack([lcg_fill(k, 700 + k + c) for c in range(n)])
+            Xd = dev(X, TORCH_DT[xdt])
+            before = ctx.fallbacks
+            out = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
+            enc.gemm(GGUFTensor("w", (k, m), ty), Xd, out, w, n)
+            torch.cuda.synchronize()
+            o = out.cpu().numpy()
+            assert np.isnan(o[n * m:]).all()
+            ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
+            assert ctx.fallbacks == before + (1 if n == 3 else 0), (k, m, n)
+            tol = gemm_tol(xdt, F32) if n > 8 else GEMV_TIGHT
+            assert rel_err(o[:n * m].reshape(n, m), ref) <= tol, (k, m, n, xdt)
     assert ctx.device_status() == 0
