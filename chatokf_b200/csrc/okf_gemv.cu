@@ -41,6 +41,7 @@ template <> struct UnitGeom<T_Q4_K> { static constexpr uint32_t bytes = 144; };
 template <> struct UnitGeom<T_Q8_0> { static constexpr uint32_t bytes = 272; };
 template <> struct UnitGeom<T_Q4_0> { static constexpr uint32_t bytes = 144; };
 template <> struct UnitGeom<T_Q6_K> { static constexpr uint32_t bytes = 210; };
+template <> struct UnitGeom<T_Q5_K> { static constexpr uint32_t bytes = 176; };
 template <> struct UnitGeom<T_Q2_0> { static constexpr uint32_t bytes = 68; };
 template <> struct UnitGeom<T_IQ2_XXS> { static constexpr uint32_t bytes = 66; };
 
@@ -241,8 +242,9 @@ struct SepConst {
 template <int TY>
 __device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_t tab, uint32_t tab_copies) {
     SepConst k = {};
-    if constexpr (TY == T_Q4_K) {
-        k.qoff = 16 + 32 * c;
+    if constexpr (TY == T_Q4_K || TY == T_Q5_K) {
+        k.qoff = (TY == T_Q4_K ? 16 : 48) + 32 * c;
+        k.hoff = 2 * c;  // Q5_K: the bit of qh that belongs to sub-block 2c
         k.sel = (c & 1) ? 0x7632u : 0x5410u;
         k.low = c < 2;
         k.m1 = k.low ? 0x3F3F3F3Fu : 0x0F0F0F0Fu;
@@ -364,6 +366,51 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
         const float db0 = f16bits(wb[0] & 0xFFFF), db1 = f16bits(wb[4] >> 16);
         acc[0] += da0 * fmaf(xs, part[0][0], -8.f * x0) + da1 * fmaf(xs, part[1][0], -8.f * x1);
         acc[1] += db0 * fmaf(xs, part[0][1], -8.f * x0) + db1 * fmaf(xs, part[1][1], -8.f * x1);
+    } else if constexpr (TY == T_Q5_K) {
+        // {f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]} (LLM/Quantize/KQuants.swift:127-158):
+        // Q4_K's header and nibbles, plus a fifth bit: bit j of qh[l] for sub-block j.  The five
+        // bits are joined into unsigned bytes (0..31) for both sub-blocks of the quarter.
+        const uint4 ha = lds128(ua), hb = lds128(ub);
+        int lo[4], hi[4];
+#pragma unroll
+        for (int half = 0; half < 2; half++) {  // 16 bytes of qs and of qh at a time
+            const uint4 a = lds128(ua + K.qoff + 16 * half), b = lds128(ub + K.qoff + 16 * half);
+            const uint4 ga = lds128(ua + 16 + 16 * half), gb = lds128(ub + 16 + 16 * half);
+            const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+            const uint32_t fa[4] = {ga.x >> K.hoff, ga.y >> K.hoff, ga.z >> K.hoff, ga.w >> K.hoff};
+            const uint32_t fb[4] = {gb.x >> K.hoff, gb.y >> K.hoff, gb.z >> K.hoff, gb.w >> K.hoff};
+            uint32_t la[4], lb[4], ua5[4], ub5[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                la[i] = (wa[i] & 0x0F0F0F0Fu) | ((fa[i] & 0x01010101u) << 4);
+                lb[i] = (wb[i] & 0x0F0F0F0Fu) | ((fb[i] & 0x01010101u) << 4);
+                ua5[i] = ((wa[i] >> 4) & 0x0F0F0F0Fu) | ((fa[i] & 0x02020202u) << 3);
+                ub5[i] = ((wb[i] >> 4) & 0x0F0F0F0Fu) | ((fb[i] & 0x02020202u) << 3);
+            }
+            if (half == 0) {
+                imma0<false>(lo, la[0], lb[0], la[1], lb[1], xf[0], xf[1]);
+                imma0<false>(hi, ua5[0], ub5[0], ua5[1], ub5[1], xf[8], xf[9]);
+                imma<false>(lo, la[2], lb[2], la[3], lb[3], xf[2], xf[3]);
+                imma<false>(hi, ua5[2], ub5[2], ua5[3], ub5[3], xf[10], xf[11]);
+            } else {
+                imma<false>(lo, la[0], lb[0], la[1], lb[1], xf[4], xf[5]);
+                imma<false>(hi, ua5[0], ub5[0], ua5[1], ub5[1], xf[12], xf[13]);
+                imma<false>(lo, la[2], lb[2], la[3], lb[3], xf[6], xf[7]);
+                imma<false>(hi, ua5[2], ub5[2], ua5[3], ub5[3], xf[14], xf[15]);
+            }
+        }
+        const uint32_t pa = prmt(ha.y, hb.y, K.sel), pb = prmt(ha.z, hb.z, K.sel), pe = prmt(ha.w, hb.w, K.sel);
+        const uint32_t sc = ((K.low ? pa : pe) & K.m1) | ((pa >> 2) & K.m2);
+        const uint32_t mn = ((K.low ? pb : (pe >> 4)) & K.m1) | ((pb >> 2) & K.m2);
+        const float la_ = join_hi_lo(lo[0], lo[1]), ha_ = join_hi_lo(hi[0], hi[1]);
+        const float lb_ = join_hi_lo(lo[2], lo[3]), hb_ = join_hi_lo(hi[2], hi[3]);
+        const float x0 = __uint_as_float(xi.y), x1 = __uint_as_float(xi.z);  // scale * sum of x per block
+        const float2 fa2 = __half22float2(*reinterpret_cast<const __half2 *>(&ha.x));
+        const float2 fb2 = __half22float2(*reinterpret_cast<const __half2 *>(&hb.x));
+        acc[0] += fa2.x * xs * (byte_to_f32(sc, 0) * la_ + byte_to_f32(sc, 1) * ha_) -
+                  fa2.y * (byte_to_f32(mn, 0) * x0 + byte_to_f32(mn, 1) * x1);
+        acc[1] += fb2.x * xs * (byte_to_f32(sc, 2) * lb_ + byte_to_f32(sc, 3) * hb_) -
+                  fb2.y * (byte_to_f32(mn, 2) * x0 + byte_to_f32(mn, 3) * x1);
     } else if constexpr (TY == T_Q6_K) {
         // {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d} (LLM/Quantize/KQuants.swift:160-177): weight =
         // d * scale[group of 16] * (q - 32), q = four bits of ql and two of qh.  Quarter c is
@@ -1348,7 +1395,7 @@ constexpr uint32_t kSharedBudget = 112 * 1024;
 
 static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, uint32_t tab_copies,
                              uint32_t budget, GemvArgs &a, GemvLayout &L) {
-    const uint32_t ub = (ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : 66;
+    const uint32_t ub = (ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : ty == T_Q5_K ? 176 : 66;
     L.nc = sep ? 1 : n;
     L.ecols = sep ? 2 : 2 * n;
     const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
@@ -1503,8 +1550,8 @@ static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int
 
 template <int TY>
 static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bool sep, cudaStream_t s, int sms, int dev) {
-    if constexpr (TY == T_Q6_K) {
-        if (!sep) return cudaErrorInvalidValue;  // no several-column kernel for this type
+    if constexpr (TY == T_Q6_K || TY == T_Q5_K) {
+        if (!sep) return cudaErrorInvalidValue;  // no several-column kernel for these types
     }
     if (sep) {
         switch (xdt) {
@@ -1512,7 +1559,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
         case DT_BF16: return launch_t<TY, DT_BF16, true>(a, G, s, sms, dev);
         case DT_F32: return launch_t<TY, DT_F32, true>(a, G, s, sms, dev);
         }
-    } else if constexpr (TY != T_Q6_K) {
+    } else if constexpr (TY != T_Q6_K && TY != T_Q5_K) {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, false>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, false>(a, G, s, sms, dev);
@@ -1525,7 +1572,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
 bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
                           const void *x, int xdt, uint32_t n, int sms) {
     if (!has_fast_kernels(ty)) return false;
-    if (ty == T_Q6_K && n > 1) return false;  // one column only: wider requests take the plain kernel
+    if ((ty == T_Q6_K || ty == T_Q5_K) && n > 1) return false;  // one column only: wider requests take the plain kernel
     if (nseg == 0 || nseg > (uint32_t)kGemvSegs || n == 0 || n > 8) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
     if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
@@ -1558,7 +1605,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
     GemvArgs a = {};
     a.status = status; a.k = k;
     a.nunit = k / 256;
-    a.row_bytes = a.nunit * ((ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : 66);
+    a.row_bytes = a.nunit * ((ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : ty == T_Q5_K ? 176 : 66);
     uint32_t tiles = 0;
     for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {
         const uint32_t j = i < nseg ? i : nseg - 1;  // unused slots repeat the last one
@@ -1602,6 +1649,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         case T_Q8_0: e = launch_ty<T_Q8_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q4_0: e = launch_ty<T_Q4_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q6_K: e = launch_ty<T_Q6_K>(a, G, xdt, sep, s, sms, dev); break;
+        case T_Q5_K: e = launch_ty<T_Q5_K>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q2_0: e = launch_ty<T_Q2_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_IQ2_XXS: e = launch_ty<T_IQ2_XXS>(a, G, xdt, sep, s, sms, dev); break;
         default: e = cudaErrorInvalidValue;

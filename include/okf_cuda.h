@@ -44,8 +44,9 @@ typedef enum okf_type {
      * Quantize/Blocks.swift:10-29; Gemma/Gemma4Quant.swift:5-49): the same entry
      * points take them, bit-exact decode included, on the plain warp-per-row /
      * fp32-tile kernels (counted by okf_fallback_count), not on the streaming
-     * integer-MMA matvec or the tensor-core tile -- except Q6_K, which has the
-     * one-column matvec (the output projection of mixed K-quant files) and the tile. */
+     * integer-MMA matvec or the tensor-core tile -- except Q5_K and Q6_K, which have
+     * the one-column matvec (mixed K-quant files keep the output projection and some
+     * other matrices in them) and the tile. */
     OKF_Q5_K = 13,    /* 176 B / 256 weights */
     OKF_Q6_K = 14,    /* 210 B / 256 weights */
     OKF_IQ4_NL = 20   /* 18 B / 32 weights, codebook of 16 values */

@@ -627,7 +627,7 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
             out = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
             enc.gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
             torch.cuda.synchronize()
-            fast = ty == GGUFType.Q4_0 or (ty == GGUFType.Q6_K and (n == 1 or n > 8))
+            fast = ty == GGUFType.Q4_0 or (ty in (GGUFType.Q6_K, GGUFType.Q5_K) and (n == 1 or n > 8))
             assert ctx.fallbacks == before + (0 if fast else 1)
             o = out.cpu().numpy()
             assert np.isnan(o[n * m:]).all()
@@ -730,14 +730,14 @@ def test_host_operator_called_again_and_again_with_the_same_buffers(ctx):
 
 
 @pytest.mark.parametrize("xdt", [F32, F16, BF16])
-def test_q6_k_one_column_matvec_and_tile(ctx, xdt):
-    """Q6_K (the output projection of mixed K-quant files; KQuant.q6K,
-    LLM/Quantize/KQuants.swift:160-177) through the integer-MMA matvec at one column and the
-    tensor-core tile above eight, against the oracle; blocks of 210 bytes leave rows and units
-    only 2-byte aligned, K short and long enough to be cut into k-chunks.  Two to eight
-    columns take the plain kernel."""
+@pytest.mark.parametrize("ty", [GGUFType.Q6_K, GGUFType.Q5_K])
+def test_q6_k_q5_k_one_column_matvec_and_tile(ctx, ty, xdt):
+    """Q6_K and Q5_K (the output projection and some FFN / attention matrices of mixed K-quant
+    files; KQuant.q5K / q6K, LLM/Quantize/KQuants.swift:127-177) through the integer-MMA matvec
+    at one column and the tensor-core tile above eight, against the oracle; Q6_K's blocks of
+    210 bytes leave rows and units only 2-byte aligned; K short and long enough to be cut into
+    k-chunks.  Two to eight columns take the plain kernel."""
     enc = CudaEnc(ctx)
-    ty = GGUFType.Q6_K
     for k, m in [(256, 16), (256, 37), (2560, 300), (5120, 1000), (9728, 205), (17408, 64)]:
         blocks = make_weights(ty, m, k, seed=k + m)
         w = ctx.upload(blocks)
