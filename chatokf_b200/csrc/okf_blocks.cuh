@@ -41,7 +41,7 @@ __host__ __device__ inline int block_bytes(int ty) {
 }
 // the types the streaming matvec and the tensor-core matmul take; the rest run on the plain kernels
 __host__ __device__ inline bool has_fast_kernels(int ty) {
-    return ty == T_Q8_0 || ty == T_Q4_K || ty == T_IQ2_XXS || ty == T_Q2_0 || ty == T_Q4_0 || ty == T_Q6_K || ty == T_Q5_K;
+    return ty == T_Q8_0 || ty == T_Q4_K || ty == T_IQ2_XXS || ty == T_Q2_0 || ty == T_Q4_0 || ty == T_Q6_K || ty == T_Q5_K || ty == T_IQ4_NL;
 }
 
 // IQ2_XXS codebook in device memory: 256 x u64 magnitudes, one copy per

@@ -887,6 +887,7 @@ cudaError_t launch_gemm_tc(int ty, const uint8_t *w, uint32_t k, uint32_t m, con
     case T_Q4_0: return tc::launch_x<T_Q4_0>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     case T_Q6_K: return tc::launch_x<T_Q6_K>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     case T_Q5_K: return tc::launch_x<T_Q5_K>(a, go, plan.nacc, xdt, odt, s, sms, dev);
+    case T_IQ4_NL: return tc::launch_x<T_IQ4_NL>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     case T_Q2_0: return tc::launch_x<T_Q2_0>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     case T_IQ2_XXS: return tc::launch_x<T_IQ2_XXS>(a, go, plan.nacc, xdt, odt, s, sms, dev);
     default: return cudaErrorInvalidValue;

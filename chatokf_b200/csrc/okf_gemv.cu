@@ -42,6 +42,7 @@ template <> struct UnitGeom<T_Q8_0> { static constexpr uint32_t bytes = 272; };
 template <> struct UnitGeom<T_Q4_0> { static constexpr uint32_t bytes = 144; };
 template <> struct UnitGeom<T_Q6_K> { static constexpr uint32_t bytes = 210; };
 template <> struct UnitGeom<T_Q5_K> { static constexpr uint32_t bytes = 176; };
+template <> struct UnitGeom<T_IQ4_NL> { static constexpr uint32_t bytes = 144; };
 template <> struct UnitGeom<T_Q2_0> { static constexpr uint32_t bytes = 68; };
 template <> struct UnitGeom<T_IQ2_XXS> { static constexpr uint32_t bytes = 66; };
 
@@ -251,7 +252,7 @@ __device__ __forceinline__ SepConst sep_const(uint32_t c, uint32_t lane, uint32_
         k.m2 = k.low ? 0u : 0x30303030u;
     } else if constexpr (TY == T_Q8_0) {
         k.qoff = 68 * c;
-    } else if constexpr (TY == T_Q4_0) {
+    } else if constexpr (TY == T_Q4_0 || TY == T_IQ4_NL) {
         k.qoff = 36 * c;
     } else if constexpr (TY == T_Q6_K) {
         k.qoff = 64 * (c >> 1);         // ql of this half of the block
@@ -278,6 +279,19 @@ __device__ __forceinline__ void iq2_sign_bytes(uint32_t idx7, uint32_t &lo, uint
     const uint32_t par = (uint32_t)__popc(idx7) << 31;
     lo = prmt(idx7 * 0x10204080u, 0u, 0xBA98u);        // signs 0..3: shifts 7, 14, 21, 28
     hi = prmt(idx7 * 0x00020408u + par, 0u, 0xBA98u);  // signs 4..6: shifts 3, 10, 17; parity on bit 31
+}
+
+// IQ4_NL: the sixteen codebook values (LLM/Gemma/Gemma4Quant.swift:5-9) for four nibbles (one per
+// byte of v, 0..15) as four signed bytes.
+__device__ __forceinline__ uint32_t iq4nl_lookup(uint32_t v) {
+    // {-127, -104, -83, -65}, {-49, -35, -22, -10}, {1, 13, 25, 38}, {53, 69, 89, 113}
+    constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;
+    const uint32_t s = v & 0x07070707u;
+    const uint32_t t = s | (s >> 4);                       // bytes 0 and 2: two selector nibbles each
+    const uint32_t sel = (t & 0xFFu) | ((t >> 8) & 0xFF00u);
+    const uint32_t lo = prmt(T0, T1, sel), hi = prmt(T2, T3, sel);
+    const uint32_t pick = ((v >> 3) & 0x01010101u) * 0xFFu;  // bytes whose nibble is 8..15
+    return (lo & ~pick) | (hi & pick);
 }
 
 // ua / ub: shared addresses of the unit in rows g and g + 8.  xf: this thread's 64
@@ -366,6 +380,45 @@ __device__ __forceinline__ void unit_sep(uint32_t ua, uint32_t ub, const SepCons
         const float db0 = f16bits(wb[0] & 0xFFFF), db1 = f16bits(wb[4] >> 16);
         acc[0] += da0 * fmaf(xs, part[0][0], -8.f * x0) + da1 * fmaf(xs, part[1][0], -8.f * x1);
         acc[1] += db0 * fmaf(xs, part[0][1], -8.f * x0) + db1 * fmaf(xs, part[1][1], -8.f * x1);
+    } else if constexpr (TY == T_IQ4_NL) {
+        // Q4_0's layout with a codebook: weight = kvalues[nibble] * d (LLM/Gemma/Gemma4Quant.swift:5-29).
+        // The sixteen signed bytes sit in four registers; a byte permute looks four nibbles up in
+        // the low or the high eight, bit 3 of each nibble picks between the two.
+        uint32_t wa[9], wb[9];
+#pragma unroll
+        for (int i = 0; i < 9; i++) {
+            wa[i] = lds32(ua + K.qoff + 4 * i);
+            wb[i] = lds32(ub + K.qoff + 4 * i);
+        }
+        uint32_t qa[8], qb[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            qa[i] = __funnelshift_r(wa[i], wa[i + 1], 16);
+            qb[i] = __funnelshift_r(wb[i], wb[i + 1], 16);
+            qa[4 + i] = wa[5 + i];
+            qb[4 + i] = wb[5 + i];
+        }
+        float part[2][2];
+#pragma unroll
+        for (int blk = 0; blk < 2; blk++) {
+            const uint32_t *a = qa + 4 * blk, *b = qb + 4 * blk;
+            const uint32_t *xb = xf + 8 * blk;  // bytes of k 0..15 (low nibbles), then 16..31 (high)
+            int d[4];
+            imma0<true>(d, iq4nl_lookup(a[0] & 0x0F0F0F0Fu), iq4nl_lookup(b[0] & 0x0F0F0F0Fu), iq4nl_lookup(a[1] & 0x0F0F0F0Fu),
+                        iq4nl_lookup(b[1] & 0x0F0F0F0Fu), xb[0], xb[1]);
+            imma<true>(d, iq4nl_lookup(a[2] & 0x0F0F0F0Fu), iq4nl_lookup(b[2] & 0x0F0F0F0Fu), iq4nl_lookup(a[3] & 0x0F0F0F0Fu),
+                       iq4nl_lookup(b[3] & 0x0F0F0F0Fu), xb[2], xb[3]);
+            imma<true>(d, iq4nl_lookup((a[0] >> 4) & 0x0F0F0F0Fu), iq4nl_lookup((b[0] >> 4) & 0x0F0F0F0Fu),
+                       iq4nl_lookup((a[1] >> 4) & 0x0F0F0F0Fu), iq4nl_lookup((b[1] >> 4) & 0x0F0F0F0Fu), xb[4], xb[5]);
+            imma<true>(d, iq4nl_lookup((a[2] >> 4) & 0x0F0F0F0Fu), iq4nl_lookup((b[2] >> 4) & 0x0F0F0F0Fu),
+                       iq4nl_lookup((a[3] >> 4) & 0x0F0F0F0Fu), iq4nl_lookup((b[3] >> 4) & 0x0F0F0F0Fu), xb[6], xb[7]);
+            part[blk][0] = join_hi_lo(d[0], d[1]);
+            part[blk][1] = join_hi_lo(d[2], d[3]);
+        }
+        const float da0 = f16bits(wa[0] & 0xFFFF), da1 = f16bits(wa[4] >> 16);
+        const float db0 = f16bits(wb[0] & 0xFFFF), db1 = f16bits(wb[4] >> 16);
+        acc[0] += xs * (da0 * part[0][0] + da1 * part[1][0]);
+        acc[1] += xs * (db0 * part[0][1] + db1 * part[1][1]);
     } else if constexpr (TY == T_Q5_K) {
         // {f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]} (LLM/Quantize/KQuants.swift:127-158):
         // Q4_K's header and nibbles, plus a fifth bit: bit j of qh[l] for sub-block j.  The five
@@ -1395,7 +1448,7 @@ constexpr uint32_t kSharedBudget = 112 * 1024;
 
 static bool gemv_layout_with(int ty, uint32_t nunit, uint32_t n, bool sep, uint32_t tiles_per_cta, uint32_t tab_copies,
                              uint32_t budget, GemvArgs &a, GemvLayout &L) {
-    const uint32_t ub = (ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : ty == T_Q5_K ? 176 : 66;
+    const uint32_t ub = (ty == T_Q4_K || ty == T_Q4_0 || ty == T_IQ4_NL) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : ty == T_Q5_K ? 176 : 66;
     L.nc = sep ? 1 : n;
     L.ecols = sep ? 2 : 2 * n;
     const uint32_t per_tile = kGemvWarps * 16 * L.nc * 4;
@@ -1550,7 +1603,7 @@ static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int
 
 template <int TY>
 static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bool sep, cudaStream_t s, int sms, int dev) {
-    if constexpr (TY == T_Q6_K || TY == T_Q5_K) {
+    if constexpr (TY == T_Q6_K || TY == T_Q5_K || TY == T_IQ4_NL) {
         if (!sep) return cudaErrorInvalidValue;  // no several-column kernel for these types
     }
     if (sep) {
@@ -1559,7 +1612,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
         case DT_BF16: return launch_t<TY, DT_BF16, true>(a, G, s, sms, dev);
         case DT_F32: return launch_t<TY, DT_F32, true>(a, G, s, sms, dev);
         }
-    } else if constexpr (TY != T_Q6_K && TY != T_Q5_K) {
+    } else if constexpr (TY != T_Q6_K && TY != T_Q5_K && TY != T_IQ4_NL) {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, false>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, false>(a, G, s, sms, dev);
@@ -1572,7 +1625,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
 bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
                           const void *x, int xdt, uint32_t n, int sms) {
     if (!has_fast_kernels(ty)) return false;
-    if ((ty == T_Q6_K || ty == T_Q5_K) && n > 1) return false;  // one column only: wider requests take the plain kernel
+    if ((ty == T_Q6_K || ty == T_Q5_K || ty == T_IQ4_NL) && n > 1) return false;  // one column only: wider requests take the plain kernel
     if (nseg == 0 || nseg > (uint32_t)kGemvSegs || n == 0 || n > 8) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
     if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
@@ -1605,7 +1658,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
     GemvArgs a = {};
     a.status = status; a.k = k;
     a.nunit = k / 256;
-    a.row_bytes = a.nunit * ((ty == T_Q4_K || ty == T_Q4_0) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : ty == T_Q5_K ? 176 : 66);
+    a.row_bytes = a.nunit * ((ty == T_Q4_K || ty == T_Q4_0 || ty == T_IQ4_NL) ? 144 : ty == T_Q8_0 ? 272 : ty == T_Q2_0 ? 68 : ty == T_Q6_K ? 210 : ty == T_Q5_K ? 176 : 66);
     uint32_t tiles = 0;
     for (uint32_t i = 0; i < (uint32_t)kGemvSegs; i++) {
         const uint32_t j = i < nseg ? i : nseg - 1;  // unused slots repeat the last one
@@ -1650,6 +1703,7 @@ cudaError_t launch_gemv_group(int ty, uint32_t nseg, const uint8_t *const *w, co
         case T_Q4_0: e = launch_ty<T_Q4_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q6_K: e = launch_ty<T_Q6_K>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q5_K: e = launch_ty<T_Q5_K>(a, G, xdt, sep, s, sms, dev); break;
+        case T_IQ4_NL: e = launch_ty<T_IQ4_NL>(a, G, xdt, sep, s, sms, dev); break;
         case T_Q2_0: e = launch_ty<T_Q2_0>(a, G, xdt, sep, s, sms, dev); break;
         case T_IQ2_XXS: e = launch_ty<T_IQ2_XXS>(a, G, xdt, sep, s, sms, dev); break;
         default: e = cudaErrorInvalidValue;

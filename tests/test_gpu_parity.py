@@ -609,10 +609,9 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
     """The types gemma trunks and mixed K-quant files add (Blocks.decoder,
     LLM/Quantize/Blocks.swift:10-29; GQ.matvec's q4_0 / iq4_nl arms,
     LLM/Gemma/Gemma4Quant.swift:93-114): the committed fixture, then 1, 4 and 33 columns
-    against the oracle.  IQ4_NL, Q5_K and Q6_K run on the warp-per-row / fp32-tile kernels
-    with exact decode, so the matvec bound applies at every width, and each call is counted
-    as a fallback; Q4_0 has the streaming matvec and the tensor-core tile, Q6_K the one-column
-    matvec and the tile."""
+    against the oracle.  Q4_0 has the streaming matvec and the tensor-core tile at every
+    width; IQ4_NL, Q5_K and Q6_K have the one-column matvec and the tile, and at two to eight
+    columns run on the warp-per-row kernel with exact decode, counted as a fallback."""
     g = golden(ty)
     k, m = int(g["k"]), int(g["m"])
     got = QB(ctx).matvec(GGUFTensor("w", (k, m), ty), ctx.upload(g["blocks"]), g["x"])
@@ -627,7 +626,7 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
             out = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
             enc.gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
             torch.cuda.synchronize()
-            fast = ty == GGUFType.Q4_0 or (ty in (GGUFType.Q6_K, GGUFType.Q5_K) and (n == 1 or n > 8))
+            fast = ty == GGUFType.Q4_0 or n == 1 or n > 8  # the others: one column and the tile
             assert ctx.fallbacks == before + (0 if fast else 1)
             o = out.cpu().numpy()
             assert np.isnan(o[n * m:]).all()
@@ -730,10 +729,11 @@ def test_host_operator_called_again_and_again_with_the_same_buffers(ctx):
 
 
 @pytest.mark.parametrize("xdt", [F32, F16, BF16])
-@pytest.mark.parametrize("ty", [GGUFType.Q6_K, GGUFType.Q5_K])
-def test_q6_k_q5_k_one_column_matvec_and_tile(ctx, ty, xdt):
+@pytest.mark.parametrize("ty", [GGUFType.Q6_K, GGUFType.Q5_K, GGUFType.IQ4_NL])
+def test_q6_k_q5_k_iq4_nl_one_column_matvec_and_tile(ctx, ty, xdt):
     """Q6_K and Q5_K (the output projection and some FFN / attention matrices of mixed K-quant
-    files; KQuant.q5K / q6K, LLM/Quantize/KQuants.swift:127-177) through the integer-MMA matvec
+    files; KQuant.q5K / q6K, LLM/Quantize/KQuants.swift:127-177) and IQ4_NL (gemma files;
+    LLM/Gemma/Gemma4Quant.swift:5-29) through the integer-MMA matvec
     at one column and the tensor-core tile above eight, against the oracle; Q6_K's blocks of
     210 bytes leave rows and units only 2-byte aligned; K short and long enough to be cut into
     k-chunks.  Two to eight columns take the plain kernel."""
