@@ -657,6 +657,63 @@ __device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, 
         auto join = [](int hi, int lo) { return fmaf((float)hi, 256.f, (float)lo); };
         acc[0] += xs * (da * (join(te[0], te[1]) + join(to[0] >> 4, to[1] >> 4)) - dma * (float)mina);
         acc[1] += xs * (db * (join(te[2], te[3]) + join(to[2] >> 4, to[3] >> 4)) - dmb * (float)minb);
+    } else if constexpr (TY == T_Q5_K) {
+        // Q4_K's layout with qh[32] after the header and a fifth bit per weight: bit j of qh[l]
+        // for sub-block j (LLM/Quantize/KQuants.swift:127-158); this thread's l are 8c .. 8c + 7
+        const uint2 ga = lds64(ua + 16 + 8 * c), gb = lds64(ub + 16 + 8 * c);
+        const uint4 ha = lds128(ua), hb = lds128(ub);
+        // 6-bit scales and mins of the eight sub-blocks, four to a word (get_scale_min_k4)
+        const uint32_t sa03 = ha.y & 0x3F3F3F3Fu, ma03 = ha.z & 0x3F3F3F3Fu;
+        const uint32_t sa47 = (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u);
+        const uint32_t ma47 = ((ha.w >> 4) & 0x0F0F0F0Fu) | ((ha.z >> 2) & 0x30303030u);
+        const uint32_t sb03 = hb.y & 0x3F3F3F3Fu, mb03 = hb.z & 0x3F3F3F3Fu;
+        const uint32_t sb47 = (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u);
+        const uint32_t mb47 = ((hb.w >> 4) & 0x0F0F0F0Fu) | ((hb.z >> 2) & 0x30303030u);
+        const int4 x03 = *reinterpret_cast<const int4 *>(xw + 4), x47 = *reinterpret_cast<const int4 *>(xw + 8);
+        const int xb[8] = {x03.x, x03.y, x03.z, x03.w, x47.x, x47.y, x47.z, x47.w};
+        const uint32_t ml = 0x0F0F0F0Fu;
+        int te[4] = {0, 0, 0, 0}, to[4] = {0, 0, 0, 0};  // sum of scale * block sum: low-nibble / high-nibble blocks
+        int mina = 0, minb = 0;
+#pragma unroll
+        for (int p = 0; p < 4; p++) {  // 32 bytes of nibbles: block 2p in the low ones, 2p+1 in the high ones
+            const uint2 wa = lds64(ua + 48 + 32 * p + 8 * c), wb = lds64(ub + 48 + 32 * p + 8 * c);
+            const uint32_t b1 = 0x01010101u;
+            const uint32_t la0 = (wa.x & ml) | (((ga.x >> (2 * p)) & b1) << 4), la1 = (wa.y & ml) | (((ga.y >> (2 * p)) & b1) << 4);
+            const uint32_t lb0 = (wb.x & ml) | (((gb.x >> (2 * p)) & b1) << 4), lb1 = (wb.y & ml) | (((gb.y >> (2 * p)) & b1) << 4);
+            const uint32_t ha0 = ((wa.x >> 4) & ml) | (((ga.x >> (2 * p + 1)) & b1) << 4), ha1 = ((wa.y >> 4) & ml) | (((ga.y >> (2 * p + 1)) & b1) << 4);
+            const uint32_t hb0 = ((wb.x >> 4) & ml) | (((gb.x >> (2 * p + 1)) & b1) << 4), hb1 = ((wb.y >> 4) & ml) | (((gb.y >> (2 * p + 1)) & b1) << 4);
+            const int sa0 = ubyte(p < 2 ? sa03 : sa47, (2 * p) & 3), sa1 = ubyte(p < 2 ? sa03 : sa47, (2 * p + 1) & 3);
+            const int sb0 = ubyte(p < 2 ? sb03 : sb47, (2 * p) & 3), sb1 = ubyte(p < 2 ? sb03 : sb47, (2 * p + 1) & 3);
+            int d[4];
+            imma0<false>(d, la0, lb0, la1, lb1, xf[4 * p], xf[4 * p + 1]);
+            te[0] += sa0 * d[0]; te[1] += sa0 * d[1]; te[2] += sb0 * d[2]; te[3] += sb0 * d[3];
+            imma0<false>(d, ha0, hb0, ha1, hb1, xf[4 * p + 2], xf[4 * p + 3]);
+            to[0] += sa1 * d[0]; to[1] += sa1 * d[1]; to[2] += sb1 * d[2]; to[3] += sb1 * d[3];
+            mina += ubyte(p < 2 ? ma03 : ma47, (2 * p) & 3) * xb[2 * p] + ubyte(p < 2 ? ma03 : ma47, (2 * p + 1) & 3) * xb[2 * p + 1];
+            minb += ubyte(p < 2 ? mb03 : mb47, (2 * p) & 3) * xb[2 * p] + ubyte(p < 2 ? mb03 : mb47, (2 * p + 1) & 3) * xb[2 * p + 1];
+        }
+        const float da = f16bits(ha.x & 0xFFFF), dma = f16bits(ha.x >> 16);
+        const float db = f16bits(hb.x & 0xFFFF), dmb = f16bits(hb.x >> 16);
+        // The scaled sums no longer fit 256 * hi + lo in 32 bits: join them in fp32.
+        auto join = [](int hi, int lo) { return fmaf((float)hi, 256.f, (float)lo); };
+        acc[0] += xs * (da * (join(te[0], te[1]) + join(to[0], to[1])) - dma * (float)mina);
+        acc[1] += xs * (db * (join(te[2], te[3]) + join(to[2], to[3])) - dmb * (float)minb);
+    } else if constexpr (TY == T_IQ4_NL) {
+        float fa = 0.f, fb = 0.f;
+        const uint32_t sh = 4 * (c >> 1);  // threads 0, 1: low nibbles (k 0..15); 2, 3: high (k 16..31)
+#pragma unroll
+        for (int b = 0; b < 8; b++) {  // block b: {f16 d; u8 qs[16]}, this thread's eight bytes at 2 + 8 (c & 1)
+            uint32_t qa[2], qb[2];
+            lds_a2<2>(ua + 18 * b + 2 + 8 * (c & 1), qa);
+            lds_a2<2>(ub + 18 * b + 2 + 8 * (c & 1), qb);
+            int d[4];
+            imma0<true>(d, iq4nl_lookup((qa[0] >> sh) & 0x0F0F0F0Fu), iq4nl_lookup((qb[0] >> sh) & 0x0F0F0F0Fu),
+                        iq4nl_lookup((qa[1] >> sh) & 0x0F0F0F0Fu), iq4nl_lookup((qb[1] >> sh) & 0x0F0F0F0Fu), xf[2 * b], xf[2 * b + 1]);
+            fa += f16bits(ld_u16(ua + 18 * b)) * join_hi_lo(d[0], d[1]);
+            fb += f16bits(ld_u16(ub + 18 * b)) * join_hi_lo(d[2], d[3]);
+        }
+        acc[0] += xs * fa;
+        acc[1] += xs * fb;
     } else if constexpr (TY == T_Q4_0) {
         const int4 x03 = *reinterpret_cast<const int4 *>(xw + 4), x47 = *reinterpret_cast<const int4 *>(xw + 8);
         const int xb[8] = {x03.x, x03.y, x03.z, x03.w, x47.x, x47.y, x47.z, x47.w};
@@ -1603,8 +1660,8 @@ static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int
 
 template <int TY>
 static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bool sep, cudaStream_t s, int sms, int dev) {
-    if constexpr (TY == T_Q6_K || TY == T_Q5_K || TY == T_IQ4_NL) {
-        if (!sep) return cudaErrorInvalidValue;  // no several-column kernel for these types
+    if constexpr (TY == T_Q6_K) {
+        if (!sep) return cudaErrorInvalidValue;  // no several-column kernel for this type
     }
     if (sep) {
         switch (xdt) {
@@ -1612,7 +1669,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
         case DT_BF16: return launch_t<TY, DT_BF16, true>(a, G, s, sms, dev);
         case DT_F32: return launch_t<TY, DT_F32, true>(a, G, s, sms, dev);
         }
-    } else if constexpr (TY != T_Q6_K && TY != T_Q5_K && TY != T_IQ4_NL) {
+    } else if constexpr (TY != T_Q6_K) {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, false>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, false>(a, G, s, sms, dev);
@@ -1625,7 +1682,7 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
 bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
                           const void *x, int xdt, uint32_t n, int sms) {
     if (!has_fast_kernels(ty)) return false;
-    if ((ty == T_Q6_K || ty == T_Q5_K || ty == T_IQ4_NL) && n > 1) return false;  // one column only: wider requests take the plain kernel
+    if (ty == T_Q6_K && n > 1) return false;  // one column only: wider requests take the plain kernel
     if (nseg == 0 || nseg > (uint32_t)kGemvSegs || n == 0 || n > 8) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
     if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;
