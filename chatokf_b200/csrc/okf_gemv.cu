@@ -714,6 +714,38 @@ __device__ __forceinline__ void unit_wide(const uint8_t *ua, const uint8_t *ub, 
         }
         acc[0] += xs * fa;
         acc[1] += xs * fb;
+    } else if constexpr (TY == T_Q6_K) {
+        // Block b = half n = b / 4 of the unit, granule r = b % 4 (see the one-column path).  This
+        // thread's eight weights l = 8c .. 8c + 7 share one of the block's two 16-wide scales,
+        // threads 0, 1 the first and 2, 3 the second: two MMAs per block, each fed by the two
+        // threads of one scale (the others pass zeros), so that each sum meets its own scale.
+        float fa = 0.f, fb = 0.f;
+        const bool first = c < 2;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            const int n = b >> 2, r = b & 3;
+            uint32_t la[2], lb[2], ha[2], hb[2];
+            lds_a2<2>(ua + 64 * n + 32 * (r & 1) + 8 * c, la);
+            lds_a2<2>(ub + 64 * n + 32 * (r & 1) + 8 * c, lb);
+            lds_a2<2>(ua + 128 + 32 * n + 8 * c, ha);
+            lds_a2<2>(ub + 128 + 32 * n + 8 * c, hb);
+            uint32_t qa[2], qb[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const uint32_t va = (((la[i] >> (r >= 2 ? 4 : 0)) & 0x0F0F0F0Fu) | (((ha[i] >> (2 * r)) & 0x03030303u) << 4)) ^ 0x20202020u;
+                const uint32_t vb = (((lb[i] >> (r >= 2 ? 4 : 0)) & 0x0F0F0F0Fu) | (((hb[i] >> (2 * r)) & 0x03030303u) << 4)) ^ 0x20202020u;
+                qa[i] = va | ((va & 0x20202020u) * 6u);  // q - 32 as a signed byte
+                qb[i] = vb | ((vb & 0x20202020u) * 6u);
+            }
+            const uint32_t sca = ld_u16(ua + 192 + 8 * n + 2 * r), scb = ld_u16(ub + 192 + 8 * n + 2 * r);
+            int d0[4], d1[4];
+            imma0<true>(d0, first ? qa[0] : 0u, first ? qb[0] : 0u, first ? qa[1] : 0u, first ? qb[1] : 0u, xf[2 * b], xf[2 * b + 1]);
+            imma0<true>(d1, first ? 0u : qa[0], first ? 0u : qb[0], first ? 0u : qa[1], first ? 0u : qb[1], xf[2 * b], xf[2 * b + 1]);
+            fa += (float)(int)(int8_t)(sca & 0xFF) * join_hi_lo(d0[0], d0[1]) + (float)(int)(int8_t)(sca >> 8) * join_hi_lo(d1[0], d1[1]);
+            fb += (float)(int)(int8_t)(scb & 0xFF) * join_hi_lo(d0[2], d0[3]) + (float)(int)(int8_t)(scb >> 8) * join_hi_lo(d1[2], d1[3]);
+        }
+        acc[0] += xs * f16bits(ld_u16(ua + 208)) * fa;
+        acc[1] += xs * f16bits(ld_u16(ub + 208)) * fb;
     } else if constexpr (TY == T_Q4_0) {
         const int4 x03 = *reinterpret_cast<const int4 *>(xw + 4), x47 = *reinterpret_cast<const int4 *>(xw + 8);
         const int xb[8] = {x03.x, x03.y, x03.z, x03.w, x47.x, x47.y, x47.z, x47.w};
@@ -1660,16 +1692,13 @@ static cudaError_t launch_t(GemvArgs a, const GemvGather &G, cudaStream_t s, int
 
 template <int TY>
 static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bool sep, cudaStream_t s, int sms, int dev) {
-    if constexpr (TY == T_Q6_K) {
-        if (!sep) return cudaErrorInvalidValue;  // no several-column kernel for this type
-    }
     if (sep) {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, true>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, true>(a, G, s, sms, dev);
         case DT_F32: return launch_t<TY, DT_F32, true>(a, G, s, sms, dev);
         }
-    } else if constexpr (TY != T_Q6_K) {
+    } else {
         switch (xdt) {
         case DT_F16: return launch_t<TY, DT_F16, false>(a, G, s, sms, dev);
         case DT_BF16: return launch_t<TY, DT_BF16, false>(a, G, s, sms, dev);
@@ -1682,7 +1711,6 @@ static cudaError_t launch_ty(const GemvArgs &a, const GemvGather &G, int xdt, bo
 bool gemv_group_supported(int ty, uint32_t k, uint32_t nseg, const uint32_t *m, const uint8_t *const *w,
                           const void *x, int xdt, uint32_t n, int sms) {
     if (!has_fast_kernels(ty)) return false;
-    if (ty == T_Q6_K && n > 1) return false;  // one column only: wider requests take the plain kernel
     if (nseg == 0 || nseg > (uint32_t)kGemvSegs || n == 0 || n > 8) return false;
     if (k % 256) return false;  // Q8_0 / Q2_0 rows that end inside a 256-wide unit take the simple kernel
     if ((uintptr_t)x % 16 || (k * (xdt == DT_F32 ? 4 : 2)) % 16) return false;

@@ -42,9 +42,7 @@ typedef enum okf_type {
     OKF_Q4_0 = 2,     /* 18 B / 32 weights (gemma trunks; Gemma/Gemma4Quant.swift:30-49) */
     /* The rest of the decoder table the trunks' files mix in (Blocks.decoder,
      * Quantize/Blocks.swift:10-29; Gemma/Gemma4Quant.swift:5-49): the same entry
-     * points take them, bit-exact decode included, on the same kernels -- except
-     * that two to eight columns of Q6_K run on the plain warp-per-row kernel
-     * (counted by okf_fallback_count). */
+     * points take them, bit-exact decode included, on the same kernels. */
     OKF_Q5_K = 13,    /* 176 B / 256 weights */
     OKF_Q6_K = 14,    /* 210 B / 256 weights */
     OKF_IQ4_NL = 20   /* 18 B / 32 weights, codebook of 16 values */

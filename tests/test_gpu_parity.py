@@ -610,8 +610,7 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
     LLM/Quantize/Blocks.swift:10-29; GQ.matvec's q4_0 / iq4_nl arms,
     LLM/Gemma/Gemma4Quant.swift:93-114): the committed fixture, then 1, 4 and 33 columns
     against the oracle.  Q4_0 has the streaming matvec and the tensor-core tile at every
-    width, and so have IQ4_NL and Q5_K; Q6_K has the one-column matvec and the tile, and at two
-    to eight columns runs on the warp-per-row kernel with exact decode, counted as a fallback."""
+    width, and so have IQ4_NL, Q5_K and Q6_K: no call here may be counted as a fallback."""
     g = golden(ty)
     k, m = int(g["k"]), int(g["m"])
     got = QB(ctx).matvec(GGUFTensor("w", (k, m), ty), ctx.upload(g["blocks"]), g["x"])
@@ -626,7 +625,7 @@ def test_more_types_golden_matvec_and_matmul(ctx, ty):
             out = torch.full((n * m + 4,), float("nan"), dtype=torch.float32, device="cuda")
             enc.gemm(GGUFTensor("w", (k, m), ty), Xd, out, ctx.upload(blocks), n)
             torch.cuda.synchronize()
-            fast = ty != GGUFType.Q6_K or n == 1 or n > 8  # Q6_K: one column and the tile only
+            fast = True  # every type of the table has the streaming matvec and the tile
             assert ctx.fallbacks == before + (0 if fast else 1)
             o = out.cpu().numpy()
             assert np.isnan(o[n * m:]).all()
@@ -730,14 +729,13 @@ def test_host_operator_called_again_and_again_with_the_same_buffers(ctx):
 
 @pytest.mark.parametrize("xdt", [F32, F16, BF16])
 @pytest.mark.parametrize("ty", [GGUFType.Q6_K, GGUFType.Q5_K, GGUFType.IQ4_NL])
-def test_q6_k_q5_k_iq4_nl_one_column_matvec_and_tile(ctx, ty, xdt):
+def test_q6_k_q5_k_iq4_nl_matvec_and_tile(ctx, ty, xdt):
     """Q6_K and Q5_K (the output projection and some FFN / attention matrices of mixed K-quant
     files; KQuant.q5K / q6K, LLM/Quantize/KQuants.swift:127-177) and IQ4_NL (gemma files;
     LLM/Gemma/Gemma4Quant.swift:5-29) through the integer-MMA matvec
-    at one column and the tensor-core tile above eight, against the oracle; Q6_K's blocks of
+    and the tensor-core tile above eight, against the oracle; Q6_K's blocks of
     210 bytes leave rows and units only 2-byte aligned; K short and long enough to be cut into
-    k-chunks.  Q5_K and IQ4_NL also have the several-column matvec; two to eight columns of
-    Q6_K take the plain kernel."""
+    k-chunks; one, three and forty columns."""
     enc = CudaEnc(ctx)
     for k, m in [(256, 16), (256, 37), (2560, 300), (5120, 1000), (9728, 205), (17408, 64)]:
         blocks = make_weights(ty, m, k, seed=k + m)
@@ -752,7 +750,7 @@ def test_q6_k_q5_k_iq4_nl_one_column_matvec_and_tile(ctx, ty, xdt):
             o = out.cpu().numpy()
             assert np.isnan(o[n * m:]).all()
             ref = oracle.matmul(ty, blocks, k, m, Xd.float().cpu().numpy(), n)
-            assert ctx.fallbacks == before + (1 if n == 3 and ty == GGUFType.Q6_K else 0), (k, m, n)
+            assert ctx.fallbacks == before, (k, m, n)
             tol = gemm_tol(xdt, F32) if n > 8 else GEMV_TIGHT
             assert rel_err(o[:n * m].reshape(n, m), ref) <= tol, (k, m, n, xdt)
     assert ctx.device_status() == 0
